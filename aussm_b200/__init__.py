@@ -1,0 +1,13 @@
+"""aussm_b200: B200 (sm_100a) implementation of the AUSSM selective-scan operators.
+
+``aussm_b200.ops`` mirrors the reference's ``extension_cpp.ops`` front end and
+calls hand-written CUDA kernels through the C ABI of ``libaussm_b200.so``
+(``include/aussm_b200.h``).  Build the library with ``python -m aussm_b200.build``.
+"""
+from . import _lib, ops
+from .ops import (device_status, install_as_extension_cpp, scan_unitary, ssm_adaptive_interface,
+                  ssm_adaptive_unitary)
+
+__version__ = "0.1.0"
+__all__ = ["ops", "ssm_adaptive_interface", "ssm_adaptive_unitary", "scan_unitary", "install_as_extension_cpp",
+           "device_status"]

@@ -1,0 +1,361 @@
+// extern "C" entry points of libaussm_b200.so (see include/aussm_b200.h) and
+// the windowed pipeline of the drop-in operators.
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+
+#include "../../include/aussm_b200.h"
+#include "projection.cuh"
+#include "scan_unitary.cuh"
+
+namespace aussm {
+
+namespace {
+thread_local std::string t_last_error;
+int g_window_override = 0;   // option "gemm_tile": steps per window of the drop-in pipeline (0 = automatic)
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    t_last_error = buf;
+}
+
+namespace {
+
+int cuda_fail(cudaError_t e, const char* what) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return AUSSM_ECUDA;
+}
+
+bool dims_ok(int B, int D, int N, int L) {
+    if (B <= 0 || D <= 0 || N <= 0 || L <= 0) {
+        set_error("sizes must be positive (B=%d D=%d N=%d L=%d)", B, D, N, L);
+        return false;
+    }
+    if (N > AUSSM_MAX_STATES) {
+        set_error("N=%d states per channel exceeds the supported maximum of %d", N, AUSSM_MAX_STATES);
+        return false;
+    }
+    if ((long long)B * D > 0x7fffffffLL) {
+        set_error("B*D=%lld channels exceed the 32-bit channel count", (long long)B * D);
+        return false;
+    }
+    return true;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ---- workspace layout of the drop-in pipeline ----
+struct Plan {
+    long long rows;      // B*D*N
+    int window;          // steps per window
+    long long ldw;       // row pitch of the window (floats)
+    size_t off_theta, off_h, off_gh, off_part, total;   // byte offsets
+};
+
+Plan make_plan(int B, int D, int N, int L) {
+    Plan p;
+    p.rows = (long long)B * D * N;
+    const long long Lp = ((long long)L + 3) / 4 * 4;
+    long long w;
+    if (g_window_override > 0) {
+        w = ((long long)g_window_override + 63) / 64 * 64;
+    } else {
+        // about 1 GiB of phases per window, at least 64 and at most 4096 steps
+        w = ((1LL << 28) / p.rows) / 64 * 64;
+        w = std::max(64LL, std::min(4096LL, w));
+    }
+    if (w >= Lp) w = Lp;
+    p.window = (int)w;
+    p.ldw = w;
+    size_t off = 0;
+    p.off_theta = off;
+    off = align_up(off + (size_t)p.rows * p.ldw * 4, 256);
+    p.off_h = off;       // re, im
+    off = align_up(off + (size_t)p.rows * 2 * 4, 256);
+    p.off_gh = off;      // re, im
+    off = align_up(off + (size_t)p.rows * 2 * 4, 256);
+    p.off_part = off;
+    off = align_up(off + scan_bwd_partial_floats((long long)B * D, N) * 4, 256);
+    p.total = off;
+    return p;
+}
+
+struct OpArgs {
+    const float *u, *dt, *x, *x_bias, *B_r, *B_theta, *C_r, *C_theta, *Dskip, *z;
+    int B, D, N, L;
+};
+
+// Forward over all windows.  y == nullptr: state only.  The final state goes
+// to (out_re, out_im), which may be the workspace pair itself.
+int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, float* y, float* out_re,
+                    float* out_im, char* ws, const Plan& pl, cudaStream_t stream) {
+    float* theta_w = reinterpret_cast<float*>(ws + pl.off_theta);
+    float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
+    float* cur_im = cur_re + pl.rows;
+    const int nwin = (a.L + pl.window - 1) / pl.window;
+    for (int w = 0; w < nwin; ++w) {
+        const long long t0 = (long long)w * pl.window;
+        const int tl = (int)std::min<long long>(pl.window, a.L - t0);
+        const ProjDims pd = {a.B, a.D, a.N, a.L, pl.ldw, t0, tl};
+        if (int rc = proj_theta(pd, a.x, a.u, theta_w, stream)) return rc;
+        const bool last = (w == nwin - 1);
+        ScanFwdParams sp = {};
+        sp.theta = theta_w;
+        sp.theta_bias = a.x_bias;
+        sp.u = a.u + t0;
+        sp.dt = a.dt + t0;
+        sp.z = a.z + t0;
+        sp.B_r = a.B_r; sp.B_theta = a.B_theta; sp.C_r = a.C_r; sp.C_theta = a.C_theta; sp.Dskip = a.Dskip;
+        sp.h0_re = (w == 0) ? h0_re : cur_re;
+        sp.h0_im = (w == 0) ? h0_im : cur_im;
+        sp.y = y ? y + t0 : nullptr;
+        sp.h1_re = last ? out_re : cur_re;
+        sp.h1_im = last ? out_im : cur_im;
+        sp.nch = a.B * a.D; sp.Dmod = a.D; sp.N = a.N; sp.L = tl;
+        sp.ld_theta = pl.ldw;
+        sp.ld_row = a.L;
+        cudaError_t e = launch_scan_unitary_fwd(sp, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "unitary scan forward launch");
+    }
+    return AUSSM_OK;
+}
+
+}  // namespace
+}  // namespace aussm
+
+using namespace aussm;
+
+extern "C" {
+
+int aussm_b200_version(void) { return 100; }
+
+const char* aussm_b200_last_error(void) { return t_last_error.c_str(); }
+
+int aussm_b200_device_status(aussm_stream_t stream) {
+    int v = 0;
+    cudaError_t e = read_and_clear_device_status((cudaStream_t)stream, &v);
+    if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+    if (v != 0) set_error("a kernel gave up waiting for a bulk copy (device status %d)", v);
+    return v;
+}
+
+int aussm_b200_set_option(const char* name, int value) {
+    if (!name) return AUSSM_EINVAL;
+    ScanOptions& o = scan_options();
+    if (!strcmp(name, "fast_trig")) o.fast_trig = value;
+    else if (!strcmp(name, "force_plain")) o.force_plain = value;
+    else if (!strcmp(name, "variant")) o.variant = value;
+    else if (!strcmp(name, "gemm_tile")) g_window_override = value;
+    else {
+        set_error("unknown option '%s'", name);
+        return AUSSM_EINVAL;
+    }
+    return AUSSM_OK;
+}
+
+int aussm_b200_scan_unitary_fwd(const float* theta, const float* u, const float* dt, const float* z,
+                                const float* B_r, const float* B_theta, const float* C_r, const float* C_theta,
+                                const float* Dskip, const float* h0_re, const float* h0_im, float* y, float* h1_re,
+                                float* h1_im, int B, int D, int N, int L, aussm_stream_t stream) {
+    if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
+    if (!theta || !u || !dt || !z || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !y) {
+        set_error("scan_unitary_fwd: null input or output pointer");
+        return AUSSM_EINVAL;
+    }
+    if ((h0_re == nullptr) != (h0_im == nullptr) || (h1_re == nullptr) != (h1_im == nullptr)) {
+        set_error("scan_unitary_fwd: real and imaginary state pointers must be given together");
+        return AUSSM_EINVAL;
+    }
+    ScanFwdParams p = {};
+    p.theta = theta; p.theta_bias = nullptr; p.u = u; p.dt = dt; p.z = z;
+    p.B_r = B_r; p.B_theta = B_theta; p.C_r = C_r; p.C_theta = C_theta; p.Dskip = Dskip;
+    p.h0_re = h0_re; p.h0_im = h0_im; p.y = y; p.h1_re = h1_re; p.h1_im = h1_im;
+    p.nch = B * D; p.Dmod = D; p.N = N; p.L = L; p.ld_theta = L; p.ld_row = L;
+    cudaError_t e = launch_scan_unitary_fwd(p, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "unitary scan forward launch");
+    return AUSSM_OK;
+}
+
+size_t aussm_b200_scan_unitary_bwd_workspace_bytes(int B, int D, int N, int L) {
+    (void)L;
+    if (B <= 0 || D <= 0 || N <= 0) return 0;
+    return align_up(scan_bwd_partial_floats((long long)B * D, N) * sizeof(float), 256);
+}
+
+int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* theta,
+                                const float* u, const float* dt, const float* z, const float* B_r,
+                                const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                                const float* h1_re, const float* h1_im, float* dtheta, float* du, float* ddt,
+                                float* dz, float* dB_r, float* dB_theta, float* dC_r, float* dC_theta, float* dD,
+                                float* dh0_re, float* dh0_im, int B, int D, int N, int L, void* workspace,
+                                size_t workspace_bytes, aussm_stream_t stream) {
+    if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
+    if (!grad_y || !theta || !u || !dt || !z || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !h1_re ||
+        !h1_im || !dtheta || !du || !ddt || !dz || !dB_r || !dB_theta || !dC_r || !dC_theta || !dD) {
+        set_error("scan_unitary_bwd: null input or output pointer");
+        return AUSSM_EINVAL;
+    }
+    if ((gh1_re == nullptr) != (gh1_im == nullptr) || (dh0_re == nullptr) != (dh0_im == nullptr)) {
+        set_error("scan_unitary_bwd: real and imaginary state pointers must be given together");
+        return AUSSM_EINVAL;
+    }
+    const size_t need = aussm_b200_scan_unitary_bwd_workspace_bytes(B, D, N, L);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
+        set_error("scan_unitary_bwd: workspace of %zu bytes (16-byte aligned) required, got %zu", need,
+                  workspace_bytes);
+        return AUSSM_EWORKSPACE;
+    }
+    const long long nch = (long long)B * D;
+    float* part_bc = static_cast<float*>(workspace);
+    float* part_d = part_bc + nch * N * 4;
+    ScanBwdParams p = {};
+    p.theta = theta; p.theta_bias = nullptr; p.u = u; p.dt = dt; p.z = z; p.gy = grad_y;
+    p.B_r = B_r; p.B_theta = B_theta; p.C_r = C_r; p.C_theta = C_theta; p.Dskip = Dskip;
+    p.h1_re = h1_re; p.h1_im = h1_im; p.gh1_re = gh1_re; p.gh1_im = gh1_im;
+    p.dtheta = dtheta; p.du = du; p.ddt = ddt; p.dz = dz; p.dh0_re = dh0_re; p.dh0_im = dh0_im;
+    p.h0_re = nullptr; p.h0_im = nullptr;
+    p.part_bc = part_bc; p.part_d = part_d; p.part_rowsum = nullptr; p.accumulate = 0;
+    p.nch = (int)nch; p.Dmod = D; p.N = N; p.L = L; p.ld_theta = L; p.ld_dtheta = L; p.ld_row = L;
+    cudaError_t e = launch_scan_unitary_bwd(p, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "unitary scan backward launch");
+    ReduceParams r = {};
+    r.part_bc = part_bc; r.part_d = part_d; r.part_rowsum = nullptr;
+    r.B_r = B_r; r.B_theta = B_theta; r.C_r = C_r; r.C_theta = C_theta;
+    r.dB_r = dB_r; r.dB_theta = dB_theta; r.dC_r = dC_r; r.dC_theta = dC_theta; r.dD = dD; r.dx_bias = nullptr;
+    r.batch = B; r.D = D; r.N = N;
+    e = launch_reduce_param_grads(r, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "parameter-gradient reduction launch");
+    return AUSSM_OK;
+}
+
+size_t aussm_b200_unitary_workspace_bytes(int B, int D, int N, int L) {
+    if (B <= 0 || D <= 0 || N <= 0 || L <= 0) return 0;
+    return make_plan(B, D, N, L).total;
+}
+
+int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, const float* x_bias, const float* B_r,
+                           const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                           const float* z, const float* h0_re, const float* h0_im, float* y, float* h1_re,
+                           float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                           aussm_stream_t stream) {
+    if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
+    if (!u || !dt || !x || !x_bias || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !z || !y) {
+        set_error("unitary_fwd: null input or output pointer");
+        return AUSSM_EINVAL;
+    }
+    if ((h0_re == nullptr) != (h0_im == nullptr) || (h1_re == nullptr) != (h1_im == nullptr)) {
+        set_error("unitary_fwd: real and imaginary state pointers must be given together");
+        return AUSSM_EINVAL;
+    }
+    const Plan pl = make_plan(B, D, N, L);
+    if (!workspace || workspace_bytes < pl.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) {
+        set_error("unitary_fwd: workspace of %zu bytes (256-byte aligned) required, got %zu", pl.total,
+                  workspace_bytes);
+        return AUSSM_EWORKSPACE;
+    }
+    char* ws = static_cast<char*>(workspace);
+    float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
+    const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
+    return run_unitary_fwd(a, h0_re, h0_im, y, h1_re ? h1_re : cur_re, h1_im ? h1_im : cur_re + pl.rows, ws, pl,
+                           (cudaStream_t)stream);
+}
+
+int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
+                           const float* dt, const float* x, const float* x_bias, const float* B_r,
+                           const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                           const float* z, const float* h0_re, const float* h0_im, const float* h1_re,
+                           const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
+                           float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
+                           float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                           aussm_stream_t stream_) {
+    if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
+    if (!grad_y || !u || !dt || !x || !x_bias || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !z || !du ||
+        !ddt || !dx || !dx_bias || !dB_r || !dB_theta || !dC_r || !dC_theta || !dD || !dz) {
+        set_error("unitary_bwd: null input or output pointer");
+        return AUSSM_EINVAL;
+    }
+    if ((gh1_re == nullptr) != (gh1_im == nullptr) || (dh0_re == nullptr) != (dh0_im == nullptr) ||
+        (h0_re == nullptr) != (h0_im == nullptr) || (h1_re == nullptr) != (h1_im == nullptr)) {
+        set_error("unitary_bwd: real and imaginary state pointers must be given together");
+        return AUSSM_EINVAL;
+    }
+    const Plan pl = make_plan(B, D, N, L);
+    if (!workspace || workspace_bytes < pl.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) {
+        set_error("unitary_bwd: workspace of %zu bytes (256-byte aligned) required, got %zu", pl.total,
+                  workspace_bytes);
+        return AUSSM_EWORKSPACE;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
+    char* ws = static_cast<char*>(workspace);
+    float* theta_w = reinterpret_cast<float*>(ws + pl.off_theta);
+    float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
+    float* cur_im = cur_re + pl.rows;
+    float* g_re = reinterpret_cast<float*>(ws + pl.off_gh);
+    float* g_im = g_re + pl.rows;
+    const long long nch = (long long)B * D;
+    float* part_bc = reinterpret_cast<float*>(ws + pl.off_part);
+    float* part_d = part_bc + nch * N * 4;
+    float* part_rowsum = part_d + nch;
+    const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
+
+    // final state: given by the caller, or recomputed by a state-only forward sweep
+    const float* hend_re = h1_re;
+    const float* hend_im = h1_im;
+    if (!h1_re) {
+        if (int rc = run_unitary_fwd(a, h0_re, h0_im, nullptr, cur_re, cur_im, ws, pl, stream)) return rc;
+        hend_re = cur_re;
+        hend_im = cur_im;
+    }
+
+    const int nwin = (L + pl.window - 1) / pl.window;
+    for (int w = nwin - 1; w >= 0; --w) {
+        const long long t0 = (long long)w * pl.window;
+        const int tl = (int)std::min<long long>(pl.window, L - t0);
+        const bool first = (w == nwin - 1);   // first processed = last in time
+        const bool final_ = (w == 0);
+        const ProjDims pd = {B, D, N, L, pl.ldw, t0, tl};
+        if (int rc = proj_theta(pd, x, u, theta_w, stream)) return rc;
+        ScanBwdParams p = {};
+        p.theta = theta_w; p.theta_bias = x_bias;
+        p.u = u + t0; p.dt = dt + t0; p.z = z + t0; p.gy = grad_y + t0;
+        p.B_r = B_r; p.B_theta = B_theta; p.C_r = C_r; p.C_theta = C_theta; p.Dskip = Dskip;
+        p.h1_re = first ? hend_re : cur_re;
+        p.h1_im = first ? hend_im : cur_im;
+        p.gh1_re = first ? gh1_re : g_re;
+        p.gh1_im = first ? gh1_im : g_im;
+        p.dtheta = theta_w;
+        p.du = du + t0; p.ddt = ddt + t0; p.dz = dz + t0;
+        p.dh0_re = final_ ? dh0_re : g_re;
+        p.dh0_im = final_ ? dh0_im : g_im;
+        p.h0_re = final_ ? nullptr : cur_re;
+        p.h0_im = final_ ? nullptr : cur_im;
+        p.part_bc = part_bc; p.part_d = part_d; p.part_rowsum = part_rowsum;
+        p.accumulate = first ? 0 : 1;
+        p.nch = (int)nch; p.Dmod = D; p.N = N; p.L = tl;
+        p.ld_theta = pl.ldw; p.ld_dtheta = pl.ldw; p.ld_row = L;
+        cudaError_t e = launch_scan_unitary_bwd(p, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "unitary scan backward launch");
+        if (int rc = proj_dx(pd, theta_w, u, dx, first, stream)) return rc;
+        if (int rc = proj_du(pd, theta_w, x, du, stream)) return rc;
+    }
+    ReduceParams r = {};
+    r.part_bc = part_bc; r.part_d = part_d; r.part_rowsum = part_rowsum;
+    r.B_r = B_r; r.B_theta = B_theta; r.C_r = C_r; r.C_theta = C_theta;
+    r.dB_r = dB_r; r.dB_theta = dB_theta; r.dC_r = dC_r; r.dC_theta = dC_theta; r.dD = dD; r.dx_bias = dx_bias;
+    r.batch = B; r.D = D; r.N = N;
+    cudaError_t e = launch_reduce_param_grads(r, stream);
+    if (e != cudaSuccess) return cuda_fail(e, "parameter-gradient reduction launch");
+    return AUSSM_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,117 @@
+/* C ABI of libaussm_b200.so: the sm_100a (B200) implementation of the AUSSM
+ * selective-scan operators.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream; it
+ * allocates nothing on the device except where noted (the cuBLAS handle of the
+ * drop-in operators is created on their first call per device), enqueues its
+ * kernels on `stream` and returns without synchronising.  Return value: 0 on
+ * success, a negative AUSSM_E* code otherwise; aussm_b200_last_error() then
+ * describes the failure (thread-local string).
+ *
+ * Tensors are float32, contiguous, row-major:
+ *   u, dt, z, y, grad_y, du, ddt, dz : (B, D, L)
+ *   theta, dtheta                    : (B, D, N, L)
+ *   x, dx                            : (D, N, D)   indexed [i][j][r]
+ *   x_bias, dx_bias                  : (D, N)
+ *   B_r, B_theta, C_r, C_theta       : (N,)        Bc = B_r exp(i B_theta), Cc likewise
+ *   Dskip                            : (D,)
+ *   hidden states and their grads    : (B, D, N)   as separate real / imaginary arrays
+ *
+ * Operator (reference: extension-cpp/extension_cpp/csrc/cuda/ssm_adaptive_unitary_forward.cu:83-181):
+ *   theta_t = sum_r x[i][j][r] u[b][r][t] + x_bias[i][j]
+ *   h_t     = exp(i theta_t) h_{t-1} + Bc_j dt_t silu(u_t)
+ *   y_t     = silu(z_t) (Dskip_i silu(u_t) + sum_j Re(Cc_j h_t))
+ */
+#ifndef AUSSM_B200_H
+#define AUSSM_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AUSSM_OK 0
+#define AUSSM_EINVAL (-1)     /* bad size, null pointer, unsupported state count */
+#define AUSSM_EWORKSPACE (-2) /* workspace missing or too small */
+#define AUSSM_ECUDA (-3)      /* a CUDA runtime or cuBLAS call failed */
+#define AUSSM_EDEVICE (-4)    /* a kernel reported a failure through the device status word */
+
+#define AUSSM_MAX_STATES 128  /* largest N the kernels are instantiated for */
+
+typedef void* aussm_stream_t; /* a cudaStream_t */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int aussm_b200_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* aussm_b200_last_error(void);
+
+/* Synchronises `stream`, then returns and clears the device status word:
+ * 0 = every kernel ran to completion, 1 = a kernel gave up on a bounded wait
+ * for a bulk copy (its outputs are then invalid). */
+int aussm_b200_device_status(aussm_stream_t stream);
+
+/* Tuning / measurement switches: name in {"fast_trig", "force_plain", "variant",
+ * "gemm_tile"}.  Returns AUSSM_EINVAL for an unknown name. */
+int aussm_b200_set_option(const char* name, int value);
+
+/* ---- scan core: the phase tensor theta is an input ----------------------
+ * The reference has no operator at this boundary (its kernels rebuild theta
+ * from x and u, ssm_adaptive_unitary_forward.cu:83-110); this is the
+ * memory-bound part of the path, split out so that it can be measured and
+ * sharded over batch x d_inner on its own. */
+int aussm_b200_scan_unitary_fwd(const float* theta, const float* u, const float* dt, const float* z,
+                                const float* B_r, const float* B_theta, const float* C_r, const float* C_theta,
+                                const float* Dskip, const float* h0_re, const float* h0_im, /* may be NULL (= 0) */
+                                float* y, float* h1_re, float* h1_im, /* h1 may be NULL */
+                                int B, int D, int N, int L, aussm_stream_t stream);
+
+/* Scratch (bytes) the backward scan needs behind `workspace`. */
+size_t aussm_b200_scan_unitary_bwd_workspace_bytes(int B, int D, int N, int L);
+
+/* h1_* is the state after the last step as returned by the forward call (the
+ * backward pass regenerates all earlier states from it); gh1_* its gradient
+ * (NULL = 0).  dtheta may alias theta.  dh0_* may be NULL. */
+int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* theta,
+                                const float* u, const float* dt, const float* z, const float* B_r,
+                                const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                                const float* h1_re, const float* h1_im, float* dtheta, float* du, float* ddt,
+                                float* dz, float* dB_r, float* dB_theta, float* dC_r, float* dC_theta, float* dD,
+                                float* dh0_re, float* dh0_im, int B, int D, int N, int L, void* workspace,
+                                size_t workspace_bytes, aussm_stream_t stream);
+
+/* ---- drop-in operators ---------------------------------------------------
+ * aussm_b200_unitary_fwd replaces ssm_adaptive_cuda_forward_unitary
+ * (ssm_adaptive_unitary_forward.cu:191-277, schema :284) and
+ * aussm_b200_unitary_bwd replaces ssm_adaptive_cuda_backward_unitary
+ * (ssm_adaptive_unitary_backward.cu:493-617, schema forward.cu:285): same
+ * inputs, same outputs, same order.  Differences a caller sees: any L in one
+ * launch sequence (the reference stops at 2048 steps per call), outputs need
+ * not be zeroed, results are deterministic, nothing synchronises the device.
+ * The phase tensor is never materialised for the whole sequence: the time
+ * axis is processed in windows through `workspace`. */
+size_t aussm_b200_unitary_workspace_bytes(int B, int D, int N, int L);
+
+int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, const float* x_bias, const float* B_r,
+                           const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                           const float* z, const float* h0_re, const float* h0_im, float* y, float* h1_re,
+                           float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                           aussm_stream_t stream);
+
+/* h1_* (the forward call's final state) may be NULL: the state is then
+ * recomputed by an extra forward sweep, as the reference's backward does
+ * (ssm_adaptive_unitary_backward.cu:50-141). */
+int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
+                           const float* dt, const float* x, const float* x_bias, const float* B_r,
+                           const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                           const float* z, const float* h0_re, const float* h0_im, const float* h1_re,
+                           const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
+                           float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
+                           float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                           aussm_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AUSSM_B200_H */

@@ -70,3 +70,38 @@ def scaled_error(got, truth):
     got = got.detach().double().cpu()
     truth = truth.detach().double().cpu()
     return float((got - truth).abs().max() / truth.abs().max().clamp_min(1e-300))
+
+
+def parity_report(name, got, truth, ref32=None, atol=1e-5, rtol=1e-4):
+    """Error of `got` against the float64 truth, next to the float32 oracle's own error."""
+    fo, mx = outside_fraction(got, truth, atol, rtol)
+    line = f"{name}: max|err|={mx:.3e} scaled={scaled_error(got, truth):.3e} outside(atol={atol},rtol={rtol})={fo:.4%}"
+    if ref32 is not None:
+        fo32, mx32 = outside_fraction(ref32, truth, atol, rtol)
+        line += f" | fp32 oracle: max|err|={mx32:.3e} outside={fo32:.4%}"
+    print(line)
+    return fo, mx
+
+
+def assert_parity(name, got, truth, ref32=None, atol=1e-5, rtol=1e-4, scaled_tol=None):
+    """Parity rule of this suite.
+
+    Pass if every element is within ``atol + rtol*|truth|`` of the float64
+    truth.  Float32 arithmetic cannot guarantee that for long sequences (the
+    reference's own float32 oracle does not meet it either), so otherwise the
+    result must be at least as close to the truth as the float32 oracle is
+    (fraction of elements outside the tolerance, and largest error), or - when
+    no float32 oracle result is at hand - within ``scaled_tol`` of the truth
+    relative to the largest magnitude of the tensor.
+    """
+    fo, mx = parity_report(name, got, truth, ref32, atol, rtol)
+    if fo == 0.0:
+        return
+    if ref32 is not None:
+        fo32, mx32 = outside_fraction(ref32, truth, atol, rtol)
+        assert fo <= max(fo32, 1e-3), f"{name}: {fo:.4%} of elements outside tolerance, float32 oracle {fo32:.4%}"
+        assert mx <= max(2.0 * mx32, atol), f"{name}: max error {mx:.3e} vs float32 oracle {mx32:.3e}"
+        return
+    assert scaled_tol is not None, f"{name}: {fo:.4%} of elements outside atol={atol} rtol={rtol}"
+    se = scaled_error(got, truth)
+    assert se <= scaled_tol, f"{name}: scaled error {se:.3e} > {scaled_tol:.1e}"

@@ -1,0 +1,130 @@
+"""Parity of the drop-in operators (extension_cpp::ssm_adaptive_unitary and its
+backward, ssm_adaptive_interface) with the reference's oracle: committed golden
+vectors and the CPU restatement on seeded inputs."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import aussm_b200
+from aussm_b200 import _lib
+from oracle import unitary as O
+from tests.helpers import NAMES, assert_parity, load_golden, model_like_inputs, scaled_error
+
+pytestmark = pytest.mark.gpu
+OPKEYS = ["u", "dt", "x", "x_bias", "B_r", "B_theta", "C_r", "C_theta", "D", "z", "h_re", "h_im"]
+
+
+def _interface_grads(inp, **kw):
+    args = [inp[k].cuda().clone().requires_grad_(True) for k in NAMES]
+    y = aussm_b200.ssm_adaptive_interface(*args, unitary=True, **kw)
+    (y * inp["gy"].cuda()).sum().backward()
+    return y.detach(), [a.grad for a in args]
+
+
+@pytest.mark.parametrize("case", ["unitary_reference_test_shape", "unitary_config0", "unitary_ragged"])
+def test_interface_matches_reference_golden(case):
+    g = load_golden(case)
+    inp = {k: g["in_" + k] for k in NAMES + ["gy"]}
+    y, grads = _interface_grads(inp)
+    assert aussm_b200.device_status() == 0
+    assert_parity("y", y, g["y_ref64"], g["y_ref32"])
+    for k, gr in zip(NAMES, grads):
+        t64, t32 = g["grad64_" + k], g["grad32_" + k]
+        if t64.is_complex():
+            gr, t64, t32 = torch.view_as_real(gr), torch.view_as_real(t64), torch.view_as_real(t32)
+        assert_parity("grad_" + k, gr, t64, t32, atol=1e-5 * float(t64.abs().max()), rtol=1e-3)
+
+
+def test_reference_test_tolerances_at_its_own_shape():
+    """The reference's test (test_extension.py:95) asks atol 7e-5 / rtol 5e-5 against its float32 oracle."""
+    g = load_golden("unitary_reference_test_shape")
+    inp = {k: g["in_" + k] for k in NAMES + ["gy"]}
+    y, grads = _interface_grads(inp, chunk_length=5)      # the ignored keyword of the reference's chunked test
+    torch.testing.assert_close(y.cpu(), g["y_ref32"], atol=7e-5, rtol=5e-5)
+    for k, gr in zip(NAMES, grads):
+        assert scaled_error(torch.view_as_real(gr) if gr.is_complex() else gr,
+                            torch.view_as_real(g["grad64_" + k]) if gr.is_complex() else g["grad64_" + k]) < 1e-5, k
+
+
+def _op_case(seed, b, d, n, l):
+    inp = model_like_inputs(seed, b, d, n, l)
+    gen = torch.Generator().manual_seed(seed + 1)
+    vals = dict(u=inp["u"], dt=inp["dt"], x=inp["x"], x_bias=inp["x_bias"],
+                B_r=F.softplus(inp["B"].real), B_theta=inp["B"].imag.clone(), C_r=F.softplus(inp["C"].real),
+                C_theta=inp["C"].imag.clone(), D=inp["D"], z=inp["z"],
+                h_re=torch.randn(b, d, n, generator=gen), h_im=torch.randn(b, d, n, generator=gen))
+    ups = dict(gy=inp["gy"], g_re=torch.randn(b, d, n, generator=gen), g_im=torch.randn(b, d, n, generator=gen))
+    return vals, ups
+
+
+def _op_oracle(vals, ups, dtype):
+    a = [vals[k].to(dtype).clone().requires_grad_(True) for k in OPKEYS]
+    y, hr, hi = O.op_unitary(*a, recurrence=(dtype == torch.float64))
+    ((y * ups["gy"].to(dtype)).sum() + (hr * ups["g_re"].to(dtype)).sum() + (hi * ups["g_im"].to(dtype)).sum()).backward()
+    return [y.detach(), hr.detach(), hi.detach()], [t.grad for t in a]
+
+
+def _op_gpu(vals, ups):
+    a = [vals[k].cuda().clone().requires_grad_(True) for k in OPKEYS]
+    y, hr, hi = aussm_b200.ssm_adaptive_unitary(*a)
+    ((y * ups["gy"].cuda()).sum() + (hr * ups["g_re"].cuda()).sum() + (hi * ups["g_im"].cuda()).sum()).backward()
+    return [y.detach(), hr.detach(), hi.detach()], [t.grad for t in a]
+
+
+@pytest.mark.parametrize("shape", [(2, 5, 4, 48), (3, 16, 16, 130), (1, 8, 8, 1), (2, 12, 32, 96), (2, 64, 16, 1024)])
+def test_operator_with_state_matches_oracle(shape):
+    vals, ups = _op_case(31 + sum(shape), *shape)
+    o64, g64 = _op_oracle(vals, ups, torch.float64)
+    o32, g32 = _op_oracle(vals, ups, torch.float32)
+    og, gg = _op_gpu(vals, ups)
+    assert aussm_b200.device_status() == 0
+    for name, p, q, r in zip(["y", "next_re", "next_im"], og, o64, o32):
+        assert_parity(name, p, q, r)
+    for k, p, q, r in zip(OPKEYS, gg, g64, g32):
+        assert_parity("grad_" + k, p, q, r, atol=1e-5 * float(q.abs().max()) + 1e-9, rtol=1e-3)
+
+
+def test_backward_operator_with_reference_schema_recomputes_the_state():
+    vals, ups = _op_case(5, 2, 6, 16, 200)
+    _, g64 = _op_oracle(vals, ups, torch.float64)
+    a = [vals[k].cuda() for k in OPKEYS]
+    grads = torch.ops.extension_cpp.ssm_adaptive_backward_unitary.default(
+        ups["gy"].cuda(), ups["g_re"].cuda(), ups["g_im"].cuda(), *a)
+    assert len(grads) == 12
+    for k, p, q in zip(OPKEYS, grads, g64):
+        assert_parity("grad_" + k, p, q, atol=1e-5 * float(q.abs().max()) + 1e-9, rtol=1e-3, scaled_tol=1e-4)
+
+
+def test_windowed_pipeline_and_chunked_front_end_agree_with_one_shot():
+    inp = model_like_inputs(77, 2, 16, 16, 328)
+    y0, g0 = _interface_grads(inp)
+    try:
+        _lib.set_option("gemm_tile", 64)              # six windows instead of one
+        y1, g1 = _interface_grads(inp)
+    finally:
+        _lib.set_option("gemm_tile", 0)
+    y2, g2 = _interface_grads(inp, max_parallel_length=80)   # python-level chunks chained through autograd
+    for y, g in ((y1, g1), (y2, g2)):
+        assert scaled_error(y, y0) < 2e-5
+        for k, p, q in zip(NAMES, g, g0):
+            if p.is_complex():
+                p, q = torch.view_as_real(p), torch.view_as_real(q)
+            assert scaled_error(p, q) < 1e-4, k
+    assert aussm_b200.device_status() == 0
+
+
+def test_extension_cpp_shim_and_errors():
+    import sys
+    pkg = aussm_b200.install_as_extension_cpp()
+    import extension_cpp
+    assert extension_cpp is pkg and extension_cpp.ops.ssm_adaptive_interface is aussm_b200.ssm_adaptive_interface
+    inp = model_like_inputs(3, 1, 4, 4, 16)
+    args = [inp[k].cuda() for k in NAMES]
+    with pytest.raises(NotImplementedError):
+        extension_cpp.ops.ssm_adaptive_interface(*args, unitary=False)
+    with pytest.raises(AssertionError):
+        extension_cpp.ops.ssm_adaptive_interface(*args, unitary=True, preal=True)
+    with pytest.raises(RuntimeError):
+        extension_cpp.ops.ssm_adaptive_interface(*[inp[k] for k in NAMES])      # CPU tensors: no fallback
+    sys.modules.pop("extension_cpp", None)
+    sys.modules.pop("extension_cpp.ops", None)
