@@ -36,11 +36,13 @@ def test_interface_matches_reference_golden(case):
 
 
 def test_reference_test_tolerances_at_its_own_shape():
-    """The reference's test (test_extension.py:95) asks atol 7e-5 / rtol 5e-5 against its float32 oracle."""
+    """The reference's test (test_extension.py:95) asks atol 7e-5 / rtol 5e-5 of its CUDA kernel against its
+    oracle.  Checked here against the float64 run of that oracle: its float32 run is itself up to 8e-4 away
+    from the float64 one on these inputs (unbounded running phase), which is more than that tolerance."""
     g = load_golden("unitary_reference_test_shape")
     inp = {k: g["in_" + k] for k in NAMES + ["gy"]}
     y, grads = _interface_grads(inp, chunk_length=5)      # the ignored keyword of the reference's chunked test
-    torch.testing.assert_close(y.cpu(), g["y_ref32"], atol=7e-5, rtol=5e-5)
+    torch.testing.assert_close(y.cpu().double(), g["y_ref64"], atol=7e-5, rtol=5e-5)
     for k, gr in zip(NAMES, grads):
         assert scaled_error(torch.view_as_real(gr) if gr.is_complex() else gr,
                             torch.view_as_real(g["grad64_" + k]) if gr.is_complex() else g["grad64_" + k]) < 1e-5, k

@@ -6,7 +6,7 @@ import torch
 import aussm_b200
 from aussm_b200 import _lib
 from oracle import unitary as O
-from tests.helpers import assert_parity, scan_core_inputs
+from tests.helpers import assert_parity, scaled_error, scan_core_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -77,9 +77,10 @@ def test_two_calls_chain_like_one():
     second = [g["theta"][..., cut:].contiguous(), g["u"][..., cut:].contiguous(), g["dt"][..., cut:].contiguous(),
               g["z"][..., cut:].contiguous()] + [g[k] for k in KEYS[4:9]] + [h1r, h1i]
     y2, h2r, h2i = aussm_b200.scan_unitary(*second)
-    torch.testing.assert_close(torch.cat([y1, y2], -1), y, rtol=1e-5, atol=1e-5)
-    torch.testing.assert_close(h2r, hr, rtol=1e-5, atol=1e-5)
-    torch.testing.assert_close(h2i, hi, rtol=1e-5, atol=1e-5)
+    # float32 rounding differs between the two decompositions: compare on the scale of the tensor
+    assert scaled_error(torch.cat([y1, y2], -1), y) < 5e-6
+    assert scaled_error(h2r, hr) < 5e-6
+    assert scaled_error(h2i, hi) < 5e-6
 
 
 def test_deterministic_and_path_independent():
@@ -109,7 +110,7 @@ def test_deterministic_and_path_independent():
         finally:
             _lib.set_option("variant", 0)
         for p, q in zip(ref, other):
-            torch.testing.assert_close(p, q, rtol=2e-4, atol=2e-4)
+            assert scaled_error(p, q) < 1e-5
     assert aussm_b200.device_status() == 0
 
 
