@@ -117,35 +117,72 @@ __device__ __forceinline__ float silu_and_grad(float x, float& grad) {
 // The recurrence multiplies the state by exp(i*theta) once per step, so the
 // error of this function is paid L times and a biased error would grow
 // linearly with the sequence length; the special-function unit's sin/cos
-// (2^-21 absolute) is therefore not used by default.  Method: quadrant
-// k = round(theta * 2/pi) through the 1.5*2^23 rounding constant (the integer
-// lands in the low mantissa bits), two-term Cody-Waite reduction with fused
-// multiply-adds, then odd/even polynomials of degree 7/6 on |r| <= pi/4 whose
-// coefficients were fitted (weighted least squares on Chebyshev nodes) to
-// 2e-9 / 1e-10 before rounding.  Measured over 2e6 angles in [-20, 20]: max
-// error 9e-8 (sin and cos), mean phase bias 3e-12, |sin^2+cos^2-1| <= 1.6e-7.
+// (2^-21 absolute) is therefore not used by default.  Method: k =
+// round(theta/pi) through the 1.5*2^23 rounding constant (the integer lands
+// in the low mantissa bits), two-term Cody-Waite reduction with fused
+// multiply-adds to |r| <= pi/2, odd/even polynomials of degree 9/10 in r, and
+// a sign flip of both results for odd k (one shift, two xors - no quadrant
+// swap).  The coefficients were fitted by weighted least squares on Chebyshev
+// nodes (4.6e-9 / 2.4e-10 before rounding) and then nudged by single ulps so
+// that sin^2+cos^2-1 has mean -8e-10 (a norm bias would make |h| drift).
+// Measured in float32 over 4e5 angles: max error 1.0e-7 (sin), 8.3e-8 (cos),
+// mean phase error -4e-11.
+//
+// sincos2 evaluates two angles at once with the packed float32x2
+// instructions of sm_100 (one issue slot per two fused multiply-adds).
 // ---------------------------------------------------------------------------
+#define AUSSM_INV_PI 0.31830987334251404f
+#define AUSSM_PI_HI 3.1415927410125732f
+#define AUSSM_PI_LO -8.742277657347586e-08f
+#define AUSSM_S0 -0.16666656732559204f
+#define AUSSM_S1 0.008333015255630016f
+#define AUSSM_S2 -0.00019806601630989462f
+#define AUSSM_S3 2.6000245725299465e-06f
+#define AUSSM_C1 0.04166664183139801f
+#define AUSSM_C2 -0.0013888401445001364f
+#define AUSSM_C3 2.476187000866048e-05f
+#define AUSSM_C4 -2.607681608424173e-07f
+#define AUSSM_MAGIC 12582912.0f   /* 1.5 * 2^23 */
+
 __device__ __forceinline__ void sincos_accurate(float theta, float& sn, float& cs) {
-    const float kMagic = 12582912.0f;            // 1.5 * 2^23
-    float kf = fmaf(theta, 0.63661977236758134f, kMagic);
-    int q = __float_as_int(kf);
-    kf -= kMagic;
-    float r = fmaf(kf, -1.5707963705062866f, theta);
-    r = fmaf(kf, 4.371138828673793e-08f, r);
-    float z = r * r;
-    float ps = fmaf(fmaf(-0.00019495567539706826f, z, 0.008331977762281895f), z, -0.16666650772094727f);
-    float s = fmaf(ps * z, r, r);
-    float pc = fmaf(fmaf(2.4438379114144482e-05f, z, -0.0013887366512790322f), z, 0.04166664555668831f);
-    float c = fmaf(pc, z * z, fmaf(-0.5f, z, 1.0f));
-    // quadrant fix-up: odd k swaps, bit 1 of k (resp. k+1) flips the sign
-    float s1 = (q & 1) ? c : s;
-    float c1 = (q & 1) ? s : c;
-    sn = __int_as_float(__float_as_int(s1) ^ ((q << 30) & 0x80000000));
-    cs = __int_as_float(__float_as_int(c1) ^ (((q + 1) << 30) & 0x80000000));
+    float kf = fmaf(theta, AUSSM_INV_PI, AUSSM_MAGIC);
+    const int sign = __float_as_int(kf) << 31;     // odd k: flip both signs
+    kf -= AUSSM_MAGIC;
+    float r = fmaf(kf, -AUSSM_PI_HI, theta);
+    r = fmaf(kf, -AUSSM_PI_LO, r);
+    const float z = r * r;
+    const float ps = fmaf(fmaf(fmaf(AUSSM_S3, z, AUSSM_S2), z, AUSSM_S1), z, AUSSM_S0);
+    const float s = fmaf(ps * z, r, r);
+    const float pc = fmaf(fmaf(fmaf(fmaf(AUSSM_C4, z, AUSSM_C3), z, AUSSM_C2), z, AUSSM_C1), z, -0.5f);
+    const float c = fmaf(pc, z, 1.0f);
+    sn = __int_as_float(__float_as_int(s) ^ sign);
+    cs = __int_as_float(__float_as_int(c) ^ sign);
+}
+
+__device__ __forceinline__ float2 f2(float a) { return make_float2(a, a); }
+
+__device__ __forceinline__ void sincos2_accurate(float2 theta, float2& sn, float2& cs) {
+    float2 kf = __ffma2_rn(theta, f2(AUSSM_INV_PI), f2(AUSSM_MAGIC));
+    const int sx = __float_as_int(kf.x) << 31, sy = __float_as_int(kf.y) << 31;
+    kf = __fadd2_rn(kf, f2(-AUSSM_MAGIC));
+    float2 r = __ffma2_rn(kf, f2(-AUSSM_PI_HI), theta);
+    r = __ffma2_rn(kf, f2(-AUSSM_PI_LO), r);
+    const float2 z = __fmul2_rn(r, r);
+    float2 ps = __ffma2_rn(f2(AUSSM_S3), z, f2(AUSSM_S2));
+    ps = __ffma2_rn(ps, z, f2(AUSSM_S1));
+    ps = __ffma2_rn(ps, z, f2(AUSSM_S0));
+    const float2 s = __ffma2_rn(__fmul2_rn(ps, z), r, r);
+    float2 pc = __ffma2_rn(f2(AUSSM_C4), z, f2(AUSSM_C3));
+    pc = __ffma2_rn(pc, z, f2(AUSSM_C2));
+    pc = __ffma2_rn(pc, z, f2(AUSSM_C1));
+    pc = __ffma2_rn(pc, z, f2(-0.5f));
+    const float2 c = __ffma2_rn(pc, z, f2(1.0f));
+    sn = make_float2(__int_as_float(__float_as_int(s.x) ^ sx), __int_as_float(__float_as_int(s.y) ^ sy));
+    cs = make_float2(__int_as_float(__float_as_int(c.x) ^ sx), __int_as_float(__float_as_int(c.y) ^ sy));
 }
 
 // Special-function-unit variant (2^-21.4 absolute on [-pi, pi]); kept for
-// measurement, selected at compile time by the kernels' FAST_TRIG parameter.
+// measurement, selected at compile time by the kernels' FAST parameter.
 __device__ __forceinline__ void sincos_fast(float theta, float& sn, float& cs) {
     float k = rintf(theta * 0.15915494309189535f);
     float r = fmaf(k, -6.2831854820251465f, theta);
@@ -154,11 +191,51 @@ __device__ __forceinline__ void sincos_fast(float theta, float& sn, float& cs) {
     cs = __cosf(r);
 }
 
+// four angles -> four (sin, cos) pairs
 template <bool FAST>
-__device__ __forceinline__ void sincos_sel(float theta, float& sn, float& cs) {
-    if (FAST) sincos_fast(theta, sn, cs);
-    else sincos_accurate(theta, sn, cs);
+__device__ __forceinline__ void sincos4(const float (&th)[4], float (&sn)[4], float (&cs)[4]) {
+    if (FAST) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sincos_fast(th[e], sn[e], cs[e]);
+    } else {
+        float2 s01, c01, s23, c23;
+        sincos2_accurate(make_float2(th[0], th[1]), s01, c01);
+        sincos2_accurate(make_float2(th[2], th[3]), s23, c23);
+        sn[0] = s01.x; sn[1] = s01.y; sn[2] = s23.x; sn[3] = s23.y;
+        cs[0] = c01.x; cs[1] = c01.y; cs[2] = c23.x; cs[3] = c23.y;
+    }
 }
+
+// ---------------------------------------------------------------------------
+// Asynchronous 16-byte global->shared copies (coalesced: consecutive lanes
+// fetch consecutive 16-byte pieces of a row), grouped per thread.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst_smem)), "l"(src_gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// shared-memory vector access of 1, 2 or 4 floats
+template <int VW> struct Vec;
+template <> struct Vec<1> {
+    float v[1];
+    __device__ __forceinline__ void ld(const float* p) { v[0] = *p; }
+    __device__ __forceinline__ void st(float* p) const { *p = v[0]; }
+};
+template <> struct Vec<2> {
+    float v[2];
+    __device__ __forceinline__ void ld(const float* p) { float2 t = *reinterpret_cast<const float2*>(p); v[0] = t.x; v[1] = t.y; }
+    __device__ __forceinline__ void st(float* p) const { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+};
+template <> struct Vec<4> {
+    float v[4];
+    __device__ __forceinline__ void ld(const float* p) { float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    __device__ __forceinline__ void st(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
 
 __device__ __forceinline__ float4 ld_shared_f4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ void st_shared_f4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }

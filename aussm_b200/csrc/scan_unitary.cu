@@ -8,20 +8,25 @@
 // csrc/cuda/ssm_adaptive_unitary_backward.cu:143-417 (the phase projection,
 // forward.cu:83-110 / backward.cu:419-490, is a separate contraction).
 //
-// Work decomposition: one thread owns SPT states of one channel and walks the
-// time axis sequentially, so the recurrence costs four fused multiply-adds
-// per step and needs no scan tree.  A warp owns 32/NL channels (NL lanes per
-// channel) and is completely independent of every other warp: it has its own
-// ring of shared-memory stages and its own mbarriers, and the kernel contains
-// no block-wide barrier.  The theta rows of a warp (contiguous in time in
-// HBM, but one row per state) are staged by bulk copies (TMA engine), each
-// lane fetching the rows it will consume, into rows padded by 16 bytes so
-// that the per-thread 128-bit shared loads of a quarter-warp hit disjoint
-// banks.  Sums over the states of a channel go through the same tile: every
-// thread overwrites the four phases it has just consumed with its four
-// contributions, and after the tile the lanes switch roles (one lane = one
-// channel and four consecutive steps) to add the NL rows and emit y with
-// 128-bit coalesced stores.
+// Work decomposition.  One thread owns SPT states of one channel and walks
+// the time axis sequentially, so the recurrence costs four fused
+// multiply-adds per step and needs no scan tree.  A warp owns 32/NL channels
+// (NL lanes per channel) and is independent of every other warp: it has its
+// own ring of shared-memory stages and the kernels contain no block-wide
+// barrier.  The theta rows of a warp (contiguous in time in HBM, one row per
+// state) are staged with 16-byte asynchronous copies, consecutive lanes
+// fetching consecutive pieces of a row (fully coalesced 128-bit loads), into
+// rows padded by 16 bytes so that the per-thread 128-bit shared loads of a
+// quarter-warp hit disjoint banks.  Sums over the states of a channel go
+// through the same tile: every thread overwrites the four phases it has just
+// consumed with its four contributions, and after the tile the lanes switch
+// roles (one lane = one channel and a few consecutive steps) to add the NL
+// rows and emit y with coalesced vector stores.
+//
+// Lanes whose state or channel does not exist (N < NL*SPT, or the last warp
+// of the grid) shadow a valid row: they load and process real data with a
+// zero output weight and store nothing, so the inner loops carry no
+// predicates.
 //
 // State normalisation: with Bc != 0 the kernels carry h/Bc instead of h, so
 // that the input term is the real number s_t (two multiply-adds less per
@@ -33,7 +38,7 @@
 // the states while it runs the adjoint recurrence
 //     eta_t = conj(Cc) w_t + exp(-i*theta_{t+1}) eta_{t+1},   w_t = gy_t silu(z_t)
 // so nothing but the inputs and the final state is ever stored.  dtheta is
-// written in place of theta in the stage and leaves by a bulk store.
+// written in place of theta in the stage and leaves with coalesced stores.
 #include "common.cuh"
 #include "scan_unitary.cuh"
 
@@ -66,37 +71,39 @@ cudaError_t read_and_clear_device_status(cudaStream_t stream, int* value) {
 
 namespace {
 
-template <int NL_, int SPT_, int T_, int STAGES_, int WARPS_>
-struct FwdCfg {
-    static constexpr int NL = NL_, SPT = SPT_, T = T_, STAGES = STAGES_, WARPS = WARPS_;
+constexpr int cmin(int a, int b) { return a < b ? a : b; }
+
+// Shape of one warp's work.  NL lanes per channel, SPT states per thread,
+// T steps per stage, TS steps per backward sub-block, AUX per-channel rows.
+template <int NL_, int SPT_, int T_, int TS_, int STAGES_, int WARPS_, int AUX_, bool BWD_>
+struct Cfg {
+    static constexpr int NL = NL_, SPT = SPT_, T = T_, TS = TS_, STAGES = STAGES_, WARPS = WARPS_, AUX = AUX_;
     static constexpr int CPW = 32 / NL;                 // channels per warp
     static constexpr int TP = T + 4;                    // padded row pitch (floats)
-    static constexpr int NROWS = 32 * SPT;
-    static constexpr int AUX = 3;                       // u, dt (becomes s), z
-    static constexpr int STAGE_FLOATS = NROWS * TP + CPW * AUX * T;
-    static constexpr int WARP_FLOATS = STAGES * STAGE_FLOATS;
-    static constexpr size_t SMEM_BYTES = (size_t)WARPS * WARP_FLOATS * sizeof(float);
-    static constexpr int NIDX = CPW * (T / 4);          // (channel, quad) items of a tile
-    static constexpr int ITERS = (NIDX + 31) / 32;
-};
-
-template <int NL_, int SPT_, int T_, int TS_, int STAGES_, int WARPS_>
-struct BwdCfg {
-    static constexpr int NL = NL_, SPT = SPT_, T = T_, TS = TS_, STAGES = STAGES_, WARPS = WARPS_;
-    static constexpr int CPW = 32 / NL;
-    static constexpr int TP = T + 4;
     static constexpr int TSP = TS + 4;
     static constexpr int NROWS = 32 * SPT;
-    static constexpr int AUX = 4;                       // u, dt, z, gy
     static constexpr int STAGE_FLOATS = NROWS * TP + CPW * AUX * T;
-    // per warp, not staged: two column-sum tiles and the s / w rows of a sub-block
-    static constexpr int SCRATCH_FLOATS = 2 * 32 * TSP + CPW * 2 * TS;
+    // backward only, not staged: two column-sum tiles and the s / w rows of a sub-block
+    static constexpr int SCRATCH_FLOATS = BWD_ ? 2 * 32 * TSP + CPW * 2 * TS : 0;
     static constexpr int WARP_FLOATS = STAGES * STAGE_FLOATS + SCRATCH_FLOATS;
     static constexpr size_t SMEM_BYTES = (size_t)WARPS * WARP_FLOATS * sizeof(float);
-    static constexpr int NIDX = CPW * (TS / 4);
-    static constexpr int ITERS = (NIDX + 31) / 32;
-    static_assert(T % TS == 0, "sub-block must divide the tile");
+    // asynchronous-copy instructions per lane and tile
+    static constexpr int CHUNKS_PER_ROW = T / 4;
+    static constexpr int NCH_THETA = NROWS * CHUNKS_PER_ROW / 32;
+    static constexpr int NCH_AUX = (CPW * AUX * CHUNKS_PER_ROW + 31) / 32;
+    // per-(channel, step) passes: every lane owns VW consecutive steps of one channel
+    static constexpr int EPL = CPW * TS / 32;           // elements per lane and sub-block
+    static constexpr int VW = cmin(4, EPL);
+    static constexpr int ITERS = EPL / VW;
+    static_assert(T % TS == 0 && T % 4 == 0 && TS % 4 == 0, "tile shape");
+    static_assert((NROWS * CHUNKS_PER_ROW) % 32 == 0, "theta chunks must fill whole warps");
+    static_assert(CPW * TS >= 32 && (CPW * TS) % 32 == 0, "pass mapping");
 };
+
+template <int NL, int SPT, int T, int STAGES, int WARPS>
+using FwdCfg = Cfg<NL, SPT, T, T, STAGES, WARPS, 3, false>;     // aux rows: u, dt (becomes s), z
+template <int NL, int SPT, int T, int TS, int STAGES, int WARPS>
+using BwdCfg = Cfg<NL, SPT, T, TS, STAGES, WARPS, 4, true>;     // aux rows: u, dt, z, gy
 
 struct StateConsts {
     float mr, mi;      // M: projection constant (Cc*Bc normalised, Cc otherwise)
@@ -159,23 +166,79 @@ __device__ __forceinline__ int slot_of(int c, int j) {
     return (j / NL) * 32 + c * NL + (j % NL);
 }
 
-// Plain (no TMA) tile load: coalesced along time, zero-filled up to a quad.
-template <int NL, int TP, int T, int AUX>
-__device__ __forceinline__ void plain_load_tile(float* th, float* aux, const float* theta, long long ld_theta,
+// Where a warp's rows live in global memory, as seen by one lane: the source
+// of every 16-byte piece this lane copies per tile (at step 0 of the launch).
+template <class C>
+struct TileMap {
+    unsigned theta_off[C::NCH_THETA];     // float offset from the warp's first theta row
+    const float* aux_ptr[C::NCH_AUX];     // per-channel rows (nullptr: this lane has no piece)
+
+    __device__ __forceinline__ void init(int lane, int nvalid, int N, long long ld_theta, long long ld_row,
+                                         long long ch0, const float* const* aux_src) {
+#pragma unroll
+        for (int i = 0; i < C::NCH_THETA; ++i) {
+            const int id = i * 32 + lane;
+            const int slot = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
+            const int k = slot / 32, w = slot % 32;
+            const int c = w / C::NL, j = (w % C::NL) + k * C::NL;
+            const bool ok = c < nvalid && j < N;
+            const long long row = ok ? (long long)c * N + j : 0;      // missing rows shadow row 0
+            theta_off[i] = (unsigned)(row * ld_theta + col * 4);
+        }
+#pragma unroll
+        for (int i = 0; i < C::NCH_AUX; ++i) {
+            const int id = i * 32 + lane;
+            const int row = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
+            aux_ptr[i] = nullptr;
+            if (row < C::CPW * C::AUX) {
+                const int cc = row / C::AUX, a = row % C::AUX;
+                const long long ch = ch0 + (cc < nvalid ? cc : 0);
+                aux_ptr[i] = aux_src[a] + ch * ld_row + col * 4;
+            }
+        }
+    }
+
+    // queue the asynchronous copies of one tile and close the group
+    __device__ __forceinline__ void issue(float* stage, const float* theta_warp, long long t0, int tlen,
+                                          int lane) const {
+        float* aux = stage + C::NROWS * C::TP;
+#pragma unroll
+        for (int i = 0; i < C::NCH_THETA; ++i) {
+            const int id = i * 32 + lane;
+            const int slot = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
+            if (col * 4 < tlen) cp_async16(stage + slot * C::TP + col * 4, theta_warp + theta_off[i] + t0);
+        }
+#pragma unroll
+        for (int i = 0; i < C::NCH_AUX; ++i) {
+            const int id = i * 32 + lane;
+            const int row = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
+            if (aux_ptr[i] != nullptr && col * 4 < tlen) cp_async16(aux + row * C::T + col * 4, aux_ptr[i] + t0);
+        }
+        cp_async_commit();
+    }
+};
+
+// Plain tile load for launches whose rows are not 16-byte aligned: coalesced
+// along time, zero-filled up to a quad, missing rows shadow row 0.
+template <class C>
+__device__ __forceinline__ void plain_load_tile(float* stage, const float* theta_warp, long long ld_theta,
                                                 const float* const* aux_src, long long ld_row, long long ch0,
                                                 int nvalid, int N, long long t0, int tlen, int lane) {
+    float* aux = stage + C::NROWS * C::TP;
     const int tq = (tlen + 3) & ~3;
-    for (int c = 0; c < nvalid; ++c) {
-        for (int j = 0; j < N; ++j) {
-            const float* src = theta + ((ch0 + c) * N + j) * ld_theta + t0;
-            float* dst = th + slot_of<NL>(c, j) * TP;
-            for (int t = lane; t < tq; t += 32) dst[t] = t < tlen ? src[t] : 0.f;
-        }
-        for (int a = 0; a < AUX; ++a) {
-            const float* src = aux_src[a] + (ch0 + c) * ld_row + t0;
-            float* dst = aux + (c * AUX + a) * T;
-            for (int t = lane; t < tq; t += 32) dst[t] = t < tlen ? src[t] : 0.f;
-        }
+    for (int slot = 0; slot < C::NROWS; ++slot) {
+        const int k = slot / 32, w = slot % 32;
+        const int c = w / C::NL, j = (w % C::NL) + k * C::NL;
+        const long long row = (c < nvalid && j < N) ? (long long)c * N + j : 0;
+        const float* src = theta_warp + row * ld_theta + t0;
+        float* dst = stage + slot * C::TP;
+        for (int t = lane; t < tq; t += 32) dst[t] = t < tlen ? src[t] : 0.f;
+    }
+    for (int row = 0; row < C::CPW * C::AUX; ++row) {
+        const int cc = row / C::AUX, a = row % C::AUX;
+        const float* src = aux_src[a] + (ch0 + (cc < nvalid ? cc : 0)) * ld_row + t0;
+        float* dst = aux + row * C::T;
+        for (int t = lane; t < tq; t += 32) dst[t] = t < tlen ? src[t] : 0.f;
     }
     __syncwarp();
 }
@@ -183,85 +246,74 @@ __device__ __forceinline__ void plain_load_tile(float* th, float* aux, const flo
 // ---------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------
-template <class C, bool BULK, bool FAST, bool NORM>
-__device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, uint64_t* wbar, long long ch0,
-                                         int nvalid, int lane, StateConsts (&sc)[C::SPT]) {
-    constexpr int NL = C::NL, SPT = C::SPT, T = C::T, TP = C::TP, STAGES = C::STAGES, CPW = C::CPW, AUX = C::AUX;
+template <class C, bool ASYNC, bool FAST, bool NORM, bool BIAS>
+__device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, long long ch0, int nvalid, int lane,
+                                         StateConsts (&sc)[C::SPT]) {
+    constexpr int NL = C::NL, SPT = C::SPT, T = C::T, TP = C::TP, STAGES = C::STAGES, AUX = C::AUX, VW = C::VW;
     const int c = lane / NL, jl = lane % NL;
     const long long ch = ch0 + c;
     const int N = p.N, L = p.L;
     const int ntiles = (L + T - 1) / T;
+    const float* theta_warp = p.theta + ch0 * N * p.ld_theta;
+    const float* aux_src[AUX] = {p.u, p.dt, p.z};
 
     float hr[SPT], hi[SPT];
-    const float* rowp[SPT];
 #pragma unroll
     for (int k = 0; k < SPT; ++k) {
         const int j = jl + k * NL;
         hr[k] = hi[k] = 0.f;
-        rowp[k] = p.theta;
         if (sc[k].act) {
-            rowp[k] = p.theta + (ch * N + j) * p.ld_theta;
             float ar = p.h0_re ? p.h0_re[ch * N + j] : 0.f;
             float ai = p.h0_im ? p.h0_im[ch * N + j] : 0.f;
             if (NORM) cdiv(ar, ai, sc[k].kr, sc[k].ki, hr[k], hi[k]);
             else { hr[k] = ar; hi[k] = ai; }
         }
     }
-    // D of the channel each post-pass item of this lane belongs to
+    // skip weight of the channel each per-(channel, step) item of this lane belongs to
     float dval[C::ITERS];
 #pragma unroll
     for (int it = 0; it < C::ITERS; ++it) {
-        const int idx = lane + 32 * it;
-        const int cc = idx / (T / 4);
-        dval[it] = (idx < C::NIDX && cc < nvalid) ? p.Dskip[(ch0 + cc) % p.Dmod] : 0.f;
+        const int cc = ((lane + 32 * it) * VW) / T;
+        dval[it] = cc < nvalid ? p.Dskip[(ch0 + cc) % p.Dmod] : 0.f;
     }
-    const float* aux_src[AUX] = {p.u, p.dt, p.z};
 
-    auto issue = [&](int tile, int stage) {
-        float* th = wsm + stage * C::STAGE_FLOATS;
-        float* aux = th + C::NROWS * TP;
-        const long long t0 = (long long)tile * T;
-        const int tlen = min(T, L - (int)t0);
-        const uint32_t bytes = (uint32_t)tlen * 4u;
-        if (lane == 0) mbar_arrive_expect_tx(&wbar[stage], (uint32_t)(nvalid * (N + AUX)) * bytes);
-        __syncwarp();
-#pragma unroll
-        for (int k = 0; k < SPT; ++k)
-            if (sc[k].act) bulk_g2s(th + (k * 32 + lane) * TP, rowp[k] + t0, bytes, &wbar[stage]);
-        if (lane < nvalid * AUX) {
-            const int cc = lane / AUX, a = lane % AUX;
-            bulk_g2s(aux + (cc * AUX + a) * T, aux_src[a] + (ch0 + cc) * p.ld_row + t0, bytes, &wbar[stage]);
+    TileMap<C> map;
+    if (ASYNC) {
+        map.init(lane, nvalid, N, p.ld_theta, p.ld_row, ch0, aux_src);
+        for (int s = 0; s < STAGES; ++s) {
+            if (s < ntiles)
+                map.issue(wsm + s * C::STAGE_FLOATS, theta_warp, (long long)s * T, min(T, L - s * T), lane);
+            else
+                cp_async_commit();
         }
-    };
-
-    if (BULK) {
-        for (int s = 0; s < STAGES && s < ntiles; ++s) issue(s, s);
     }
 
     for (int tile = 0; tile < ntiles; ++tile) {
-        const int stage = BULK ? tile % STAGES : 0;
+        const int stage = ASYNC ? tile % STAGES : 0;
         float* th = wsm + stage * C::STAGE_FLOATS;
         float* aux = th + C::NROWS * TP;
         const long long t0 = (long long)tile * T;
         const int tlen = min(T, L - (int)t0);
         const int nq = (tlen + 3) >> 2;
-        if (BULK) {
-            if (!mbar_wait_bounded(&wbar[stage], (uint32_t)(tile / STAGES) & 1u, p.status)) return;
+        if (ASYNC) {
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
         } else {
-            plain_load_tile<NL, TP, T, AUX>(th, aux, p.theta, p.ld_theta, aux_src, p.ld_row, ch0, nvalid, N, t0,
-                                            tlen, lane);
+            plain_load_tile<C>(th, theta_warp, p.ld_theta, aux_src, p.ld_row, ch0, nvalid, N, t0, tlen, lane);
         }
 
         // pre-pass: s = dt * silu(u) over the dt row
 #pragma unroll
         for (int it = 0; it < C::ITERS; ++it) {
-            const int idx = lane + 32 * it;
-            const int cc = idx / (T / 4), q = idx % (T / 4);
-            if (idx < C::NIDX && cc < nvalid && q < nq) {
-                float4 u4 = ld_shared_f4(aux + (cc * AUX + 0) * T + 4 * q);
-                float4 d4 = ld_shared_f4(aux + (cc * AUX + 1) * T + 4 * q);
-                d4.x *= siluf_(u4.x); d4.y *= siluf_(u4.y); d4.z *= siluf_(u4.z); d4.w *= siluf_(u4.w);
-                st_shared_f4(aux + (cc * AUX + 1) * T + 4 * q, d4);
+            const int e0 = (lane + 32 * it) * VW;
+            const int cc = e0 / T, t = e0 % T;
+            if (t < tlen) {
+                Vec<VW> u, d;
+                u.ld(aux + (cc * AUX + 0) * T + t);
+                d.ld(aux + (cc * AUX + 1) * T + t);
+#pragma unroll
+                for (int e = 0; e < VW; ++e) d.v[e] *= siluf_(u.v[e]);
+                d.st(aux + (cc * AUX + 1) * T + t);
             }
         }
         __syncwarp();
@@ -271,72 +323,81 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, uin
         for (int q = 0; q < nq; ++q) {
             const float4 s4 = ld_shared_f4(srow + 4 * q);
             const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-            float pacc[4] = {0.f, 0.f, 0.f, 0.f};
+            float pacc[4];
 #pragma unroll
             for (int k = 0; k < SPT; ++k) {
-                float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (sc[k].act) t4 = ld_shared_f4(th + (k * 32 + lane) * TP + 4 * q);
-                const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+                const float4 t4 = ld_shared_f4(th + (k * 32 + lane) * TP + 4 * q);
+                float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+                if (BIAS) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) tv[e] += sc[k].bias;
+                }
+                float sn[4], cs[4];
+                sincos4<FAST>(tv, sn, cs);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    if (!BULK && 4 * q + e >= tlen) continue;   // ragged tail (plain path only)
-                    float sn, cs;
-                    sincos_sel<FAST>(tv[e] + sc[k].bias, sn, cs);
+                    if (!ASYNC && 4 * q + e >= tlen) {           // ragged tail (plain path only)
+                        if (k == 0) pacc[e] = 0.f;
+                        continue;
+                    }
                     float nr, ni;
                     if (NORM) {
-                        nr = fmaf(cs, hr[k], fmaf(-sn, hi[k], sv[e]));
-                        ni = fmaf(cs, hi[k], sn * hr[k]);
+                        nr = fmaf(cs[e], hr[k], fmaf(-sn[e], hi[k], sv[e]));
+                        ni = fmaf(cs[e], hi[k], sn[e] * hr[k]);
                     } else {
-                        nr = fmaf(cs, hr[k], fmaf(-sn, hi[k], sc[k].br * sv[e]));
-                        ni = fmaf(cs, hi[k], fmaf(sn, hr[k], sc[k].bi * sv[e]));
+                        nr = fmaf(cs[e], hr[k], fmaf(-sn[e], hi[k], sc[k].br * sv[e]));
+                        ni = fmaf(cs[e], hi[k], fmaf(sn[e], hr[k], sc[k].bi * sv[e]));
                     }
                     hr[k] = nr;
                     hi[k] = ni;
-                    pacc[e] += fmaf(sc[k].mr, nr, -sc[k].mi * ni);
+                    const float pv = fmaf(sc[k].mr, nr, -sc[k].mi * ni);
+                    pacc[e] = (k == 0) ? pv : pacc[e] + pv;
                 }
             }
             st_shared_f4(th + lane * TP + 4 * q, make_float4(pacc[0], pacc[1], pacc[2], pacc[3]));
         }
         __syncwarp();
 
-        // post-pass: one lane = one channel and four steps
+        // post-pass: one lane = one channel and VW steps
         if (p.y) {
 #pragma unroll
             for (int it = 0; it < C::ITERS; ++it) {
-                const int idx = lane + 32 * it;
-                const int cc = idx / (T / 4), q = idx % (T / 4);
-                if (idx < C::NIDX && cc < nvalid && q < nq) {
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                const int e0 = (lane + 32 * it) * VW;
+                const int cc = e0 / T, t = e0 % T;
+                if (t < tlen && cc < nvalid) {
+                    Vec<VW> acc, u, z;
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) acc.v[e] = 0.f;
 #pragma unroll
                     for (int r = 0; r < NL; ++r) {
-                        float4 v = ld_shared_f4(th + (cc * NL + r) * TP + 4 * q);
-                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                        Vec<VW> v;
+                        v.ld(th + (cc * NL + r) * TP + t);
+#pragma unroll
+                        for (int e = 0; e < VW; ++e) acc.v[e] += v.v[e];
                     }
-                    const float4 u4 = ld_shared_f4(aux + (cc * AUX + 0) * T + 4 * q);
-                    const float4 z4 = ld_shared_f4(aux + (cc * AUX + 2) * T + 4 * q);
-                    const float dv = dval[it];
-                    float4 y4;
-                    y4.x = siluf_(z4.x) * fmaf(dv, siluf_(u4.x), acc.x);
-                    y4.y = siluf_(z4.y) * fmaf(dv, siluf_(u4.y), acc.y);
-                    y4.z = siluf_(z4.z) * fmaf(dv, siluf_(u4.z), acc.z);
-                    y4.w = siluf_(z4.w) * fmaf(dv, siluf_(u4.w), acc.w);
-                    float* dst = p.y + (ch0 + cc) * p.ld_row + t0 + 4 * q;
-                    if (BULK) {
-                        *reinterpret_cast<float4*>(dst) = y4;
+                    u.ld(aux + (cc * AUX + 0) * T + t);
+                    z.ld(aux + (cc * AUX + 2) * T + t);
+#pragma unroll
+                    for (int e = 0; e < VW; ++e)
+                        acc.v[e] = siluf_(z.v[e]) * fmaf(dval[it], siluf_(u.v[e]), acc.v[e]);
+                    float* dst = p.y + (ch0 + cc) * p.ld_row + t0 + t;
+                    if (ASYNC) {
+                        acc.st(dst);      // global pointers take the same vector stores
                     } else {
-                        const float yv[4] = {y4.x, y4.y, y4.z, y4.w};
-                        for (int e = 0; e < 4; ++e)
-                            if (4 * q + e < tlen) dst[e] = yv[e];
+                        for (int e = 0; e < VW; ++e)
+                            if (t + e < tlen) dst[e] = acc.v[e];
                     }
                 }
             }
         }
         __syncwarp();
-        if (BULK && tile + STAGES < ntiles) {
-            fence_proxy_async();
-            issue(tile + STAGES, stage);
+        if (ASYNC) {
+            const int nt = tile + STAGES;
+            if (nt < ntiles) map.issue(th, theta_warp, (long long)nt * T, min(T, L - nt * T), lane);
+            else cp_async_commit();
         }
     }
+    if (ASYNC) cp_async_wait<0>();
 
 #pragma unroll
     for (int k = 0; k < SPT; ++k) {
@@ -353,24 +414,14 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, uin
     }
 }
 
-template <class C, bool BULK, bool FAST>
+template <class C, bool ASYNC, bool FAST, bool BIAS>
 __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const ScanFwdParams p) {
     extern __shared__ __align__(128) float smem[];
-    __shared__ uint64_t bars[C::WARPS * C::STAGES];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long ch0 = ((long long)blockIdx.x * C::WARPS + warp) * C::CPW;
     if (ch0 >= p.nch) return;   // warps never meet at a block barrier
     const int nvalid = (int)min((long long)C::CPW, (long long)p.nch - ch0);
     float* wsm = smem + (size_t)warp * C::WARP_FLOATS;
-    uint64_t* wbar = bars + warp * C::STAGES;
-    if (BULK) {
-        if (lane == 0) {
-            for (int s = 0; s < C::STAGES; ++s) mbar_init(&wbar[s], 1);
-            fence_mbar_init();
-            fence_proxy_async();
-        }
-        __syncwarp();
-    }
     const int c = lane / C::NL, jl = lane % C::NL;
     const int i = (int)((ch0 + min(c, nvalid - 1)) % p.Dmod);
     StateConsts sc[C::SPT];
@@ -380,7 +431,7 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const S
         const int j = jl + k * C::NL;
         bool okk;
         load_state_consts(sc[k], c < nvalid && j < p.N, j, i, p.N, p.B_r, p.B_theta, p.C_r, p.C_theta,
-                          p.theta_bias, okk);
+                          BIAS ? p.theta_bias : nullptr, okk);
         ok = ok && okk;
     }
     if (__all_sync(0xffffffffu, ok)) {
@@ -389,25 +440,27 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const S
             float a, b;
             normalise_consts(sc[k], a, b);
         }
-        fwd_warp<C, BULK, FAST, true>(p, wsm, wbar, ch0, nvalid, lane, sc);
+        fwd_warp<C, ASYNC, FAST, true, BIAS>(p, wsm, ch0, nvalid, lane, sc);
     } else {
-        fwd_warp<C, BULK, FAST, false>(p, wsm, wbar, ch0, nvalid, lane, sc);
+        fwd_warp<C, ASYNC, FAST, false, BIAS>(p, wsm, ch0, nvalid, lane, sc);
     }
 }
 
 // ---------------------------------------------------------------------------
 // Backward
 // ---------------------------------------------------------------------------
-template <class C, bool BULK, bool FAST, bool NORM>
-__device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uint64_t* wbar, long long ch0,
-                                         int nvalid, int lane, StateConsts (&sc)[C::SPT],
-                                         const float (&ccr)[C::SPT], const float (&cci)[C::SPT]) {
+template <class C, bool ASYNC, bool FAST, bool NORM, bool BIAS>
+__device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, long long ch0, int nvalid, int lane,
+                                         StateConsts (&sc)[C::SPT], const float (&ccr)[C::SPT],
+                                         const float (&cci)[C::SPT]) {
     constexpr int NL = C::NL, SPT = C::SPT, T = C::T, TS = C::TS, TP = C::TP, TSP = C::TSP, STAGES = C::STAGES,
-                  CPW = C::CPW, AUX = C::AUX;
+                  AUX = C::AUX, VW = C::VW;
     const int c = lane / NL, jl = lane % NL;
     const long long ch = ch0 + c;
     const int N = p.N, L = p.L;
     const int ntiles = (L + T - 1) / T;
+    const float* theta_warp = p.theta + ch0 * N * p.ld_theta;
+    float* dtheta_warp = p.dtheta + ch0 * N * p.ld_theta;       // launcher guarantees equal pitches
 
     float* scratch = wsm + STAGES * C::STAGE_FLOATS;
     float* pt = scratch;                    // [32][TSP] projections, summed over a thread's states
@@ -420,17 +473,11 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uin
     float sbr[SPT], sbi[SPT];   // sum_t eta_t s_t              (general representation only)
     float rsum[SPT];            // sum_t dtheta_t
     float hlr[SPT], hli[SPT];   // conj(h_{L-1}) . gh   (boundary term of the Bc gradient)
-    const float* rowp[SPT];
-    float* drowp[SPT];
 #pragma unroll
     for (int k = 0; k < SPT; ++k) {
         const int j = jl + k * NL;
         hr[k] = hi[k] = er[k] = ei[k] = gmr[k] = gmi[k] = sbr[k] = sbi[k] = rsum[k] = hlr[k] = hli[k] = 0.f;
-        rowp[k] = p.theta;
-        drowp[k] = p.dtheta;
         if (sc[k].act) {
-            rowp[k] = p.theta + (ch * N + j) * p.ld_theta;
-            drowp[k] = p.dtheta + (ch * N + j) * p.ld_dtheta;
             const float ar = p.h1_re[ch * N + j], ai = p.h1_im[ch * N + j];
             const float gr = p.gh1_re ? p.gh1_re[ch * N + j] : 0.f;
             const float gi = p.gh1_im ? p.gh1_im[ch * N + j] : 0.f;
@@ -450,47 +497,37 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uin
     float dval[C::ITERS], dacc[C::ITERS];
 #pragma unroll
     for (int it = 0; it < C::ITERS; ++it) {
-        const int idx = lane + 32 * it;
-        const int cc = idx / (TS / 4);
-        dval[it] = (idx < C::NIDX && cc < nvalid) ? p.Dskip[(ch0 + cc) % p.Dmod] : 0.f;
+        const int cc = ((lane + 32 * it) * VW) / TS;
+        dval[it] = cc < nvalid ? p.Dskip[(ch0 + cc) % p.Dmod] : 0.f;
         dacc[it] = 0.f;
     }
     const float* aux_src[AUX] = {p.u, p.dt, p.z, p.gy};
 
-    auto issue = [&](int tile, int stage) {
-        float* th = wsm + stage * C::STAGE_FLOATS;
-        float* aux = th + C::NROWS * TP;
-        const long long t0 = (long long)tile * T;
-        const int tlen = min(T, L - (int)t0);
-        const uint32_t bytes = (uint32_t)tlen * 4u;
-        if (lane == 0) mbar_arrive_expect_tx(&wbar[stage], (uint32_t)(nvalid * (N + AUX)) * bytes);
-        __syncwarp();
-#pragma unroll
-        for (int k = 0; k < SPT; ++k)
-            if (sc[k].act) bulk_g2s(th + (k * 32 + lane) * TP, rowp[k] + t0, bytes, &wbar[stage]);
-        if (lane < nvalid * AUX) {
-            const int cc = lane / AUX, a = lane % AUX;
-            bulk_g2s(aux + (cc * AUX + a) * T, aux_src[a] + (ch0 + cc) * p.ld_row + t0, bytes, &wbar[stage]);
-        }
-    };
-
     // r counts tiles in processing order (last tile first)
-    if (BULK) {
-        for (int r = 0; r < STAGES && r < ntiles; ++r) issue(ntiles - 1 - r, r);
+    TileMap<C> map;
+    if (ASYNC) {
+        map.init(lane, nvalid, N, p.ld_theta, p.ld_row, ch0, aux_src);
+        for (int r = 0; r < STAGES; ++r) {
+            const int tile = ntiles - 1 - r;
+            if (tile >= 0)
+                map.issue(wsm + r * C::STAGE_FLOATS, theta_warp, (long long)tile * T, min(T, L - tile * T), lane);
+            else
+                cp_async_commit();
+        }
     }
 
     for (int r = 0; r < ntiles; ++r) {
         const int tile = ntiles - 1 - r;
-        const int stage = BULK ? r % STAGES : 0;
+        const int stage = ASYNC ? r % STAGES : 0;
         float* th = wsm + stage * C::STAGE_FLOATS;
         float* aux = th + C::NROWS * TP;
         const long long t0 = (long long)tile * T;
         const int tlen = min(T, L - (int)t0);
-        if (BULK) {
-            if (!mbar_wait_bounded(&wbar[stage], (uint32_t)(r / STAGES) & 1u, p.status)) break;
+        if (ASYNC) {
+            cp_async_wait<STAGES - 1>();
+            __syncwarp();
         } else {
-            plain_load_tile<NL, TP, T, AUX>(th, aux, p.theta, p.ld_theta, aux_src, p.ld_row, ch0, nvalid, N, t0,
-                                            tlen, lane);
+            plain_load_tile<C>(th, theta_warp, p.ld_theta, aux_src, p.ld_row, ch0, nvalid, N, t0, tlen, lane);
         }
 
         const int nsb = (tlen + TS - 1) / TS;
@@ -498,25 +535,26 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uin
             const int sbeg = sb * TS;                       // first step of the sub-block in the tile
             const int slen = min(TS, tlen - sbeg);
             const int nq = (slen + 3) >> 2;
-            const int qoff = sbeg >> 2;                     // quad offset inside the tile
 
             // pre-pass: s = dt silu(u), w = gy silu(z)
 #pragma unroll
             for (int it = 0; it < C::ITERS; ++it) {
-                const int idx = lane + 32 * it;
-                const int cc = idx / (TS / 4), q = idx % (TS / 4);
-                if (idx < C::NIDX && cc < nvalid && q < nq) {
-                    const int o = 4 * (qoff + q);
-                    const float4 u4 = ld_shared_f4(aux + (cc * AUX + 0) * T + o);
-                    const float4 d4 = ld_shared_f4(aux + (cc * AUX + 1) * T + o);
-                    const float4 z4 = ld_shared_f4(aux + (cc * AUX + 2) * T + o);
-                    const float4 g4 = ld_shared_f4(aux + (cc * AUX + 3) * T + o);
-                    st_shared_f4(sw + (cc * 2 + 0) * TS + 4 * q,
-                                 make_float4(d4.x * siluf_(u4.x), d4.y * siluf_(u4.y), d4.z * siluf_(u4.z),
-                                             d4.w * siluf_(u4.w)));
-                    st_shared_f4(sw + (cc * 2 + 1) * TS + 4 * q,
-                                 make_float4(g4.x * siluf_(z4.x), g4.y * siluf_(z4.y), g4.z * siluf_(z4.z),
-                                             g4.w * siluf_(z4.w)));
+                const int e0 = (lane + 32 * it) * VW;
+                const int cc = e0 / TS, t = e0 % TS;
+                if (t < slen) {
+                    const int o = sbeg + t;
+                    Vec<VW> u, d, z, g;
+                    u.ld(aux + (cc * AUX + 0) * T + o);
+                    d.ld(aux + (cc * AUX + 1) * T + o);
+                    z.ld(aux + (cc * AUX + 2) * T + o);
+                    g.ld(aux + (cc * AUX + 3) * T + o);
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) {
+                        d.v[e] *= siluf_(u.v[e]);
+                        g.v[e] *= siluf_(z.v[e]);
+                    }
+                    d.st(sw + (cc * 2 + 0) * TS + t);
+                    g.st(sw + (cc * 2 + 1) * TS + t);
                 }
             }
             __syncwarp();
@@ -527,20 +565,26 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uin
                 const float4 w4 = ld_shared_f4(sw + (c * 2 + 1) * TS + 4 * q);
                 const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
                 const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
-                float pacc[4] = {0.f, 0.f, 0.f, 0.f};
-                float eacc[4] = {0.f, 0.f, 0.f, 0.f};
+                float pacc[4], eacc[4];
 #pragma unroll
                 for (int k = 0; k < SPT; ++k) {
-                    float* cell = th + (k * 32 + lane) * TP + 4 * (qoff + q);
-                    float4 t4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (sc[k].act) t4 = ld_shared_f4(cell);
-                    const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
-                    float dth[4] = {0.f, 0.f, 0.f, 0.f};
+                    float* cell = th + (k * 32 + lane) * TP + sbeg + 4 * q;
+                    const float4 t4 = ld_shared_f4(cell);
+                    float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+                    if (BIAS) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) tv[e] += sc[k].bias;
+                    }
+                    float sn[4], cs[4];
+                    sincos4<FAST>(tv, sn, cs);
+                    float dth[4];
 #pragma unroll
                     for (int e = 3; e >= 0; --e) {
-                        if (!BULK && 4 * q + e >= slen) continue;
-                        float sn, cs;
-                        sincos_sel<FAST>(tv[e] + sc[k].bias, sn, cs);
+                        if (!ASYNC && 4 * q + e >= slen) {
+                            dth[e] = 0.f;
+                            if (k == 0) { pacc[e] = 0.f; eacc[e] = 0.f; }
+                            continue;
+                        }
                         const float w = wv[e], s = sv[e];
                         // eta_t = carry + conj(M) w
                         const float nr = fmaf(sc[k].mr, w, er[k]);
@@ -552,73 +596,73 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uin
                         // dtheta_t = -Im(conj(eta) a)
                         const float d = fmaf(ni, ar, -nr * ai);
                         dth[e] = d;
-                        rsum[k] += d;
-                        pacc[e] += fmaf(sc[k].mr, hr[k], -sc[k].mi * hi[k]);
+                        if (BIAS) rsum[k] += d;
+                        const float pv = fmaf(sc[k].mr, hr[k], -sc[k].mi * hi[k]);
                         // gradient of the real drive s_t: Re(conj(eta) beta)
-                        if (NORM) eacc[e] += nr;
-                        else eacc[e] += fmaf(nr, sc[k].br, ni * sc[k].bi);
+                        const float ev = NORM ? nr : fmaf(nr, sc[k].br, ni * sc[k].bi);
+                        pacc[e] = (k == 0) ? pv : pacc[e] + pv;
+                        eacc[e] = (k == 0) ? ev : eacc[e] + ev;
                         gmr[k] = fmaf(w, hr[k], gmr[k]);
                         gmi[k] = fmaf(-w, hi[k], gmi[k]);
                         if (!NORM) { sbr[k] = fmaf(nr, s, sbr[k]); sbi[k] = fmaf(ni, s, sbi[k]); }
                         // step back: h_{t-1} = conj(lambda) a ; carry = conj(lambda) eta
-                        hr[k] = fmaf(cs, ar, sn * ai);
-                        hi[k] = fmaf(cs, ai, -sn * ar);
-                        er[k] = fmaf(cs, nr, sn * ni);
-                        ei[k] = fmaf(cs, ni, -sn * nr);
+                        hr[k] = fmaf(cs[e], ar, sn[e] * ai);
+                        hi[k] = fmaf(cs[e], ai, -sn[e] * ar);
+                        er[k] = fmaf(cs[e], nr, sn[e] * ni);
+                        ei[k] = fmaf(cs[e], ni, -sn[e] * nr);
                     }
-                    if (sc[k].act) st_shared_f4(cell, make_float4(dth[0], dth[1], dth[2], dth[3]));
+                    st_shared_f4(cell, make_float4(dth[0], dth[1], dth[2], dth[3]));
                 }
                 st_shared_f4(pt + lane * TSP + 4 * q, make_float4(pacc[0], pacc[1], pacc[2], pacc[3]));
                 st_shared_f4(et + lane * TSP + 4 * q, make_float4(eacc[0], eacc[1], eacc[2], eacc[3]));
             }
             __syncwarp();
 
-            // post-pass: du, ddt, dz for one channel and four steps per lane
+            // post-pass: du, ddt, dz for one channel and VW steps per lane
 #pragma unroll
             for (int it = 0; it < C::ITERS; ++it) {
-                const int idx = lane + 32 * it;
-                const int cc = idx / (TS / 4), q = idx % (TS / 4);
-                if (idx < C::NIDX && cc < nvalid && q < nq) {
-                    float4 P = make_float4(0.f, 0.f, 0.f, 0.f), E = P;
+                const int e0 = (lane + 32 * it) * VW;
+                const int cc = e0 / TS, t = e0 % TS;
+                if (t < slen && cc < nvalid) {
+                    Vec<VW> P, E, u, d, z, g, du, ddt, dz;
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) P.v[e] = E.v[e] = 0.f;
 #pragma unroll
                     for (int rr = 0; rr < NL; ++rr) {
-                        const float4 a = ld_shared_f4(pt + (cc * NL + rr) * TSP + 4 * q);
-                        const float4 b = ld_shared_f4(et + (cc * NL + rr) * TSP + 4 * q);
-                        P.x += a.x; P.y += a.y; P.z += a.z; P.w += a.w;
-                        E.x += b.x; E.y += b.y; E.z += b.z; E.w += b.w;
+                        Vec<VW> a, b;
+                        a.ld(pt + (cc * NL + rr) * TSP + t);
+                        b.ld(et + (cc * NL + rr) * TSP + t);
+#pragma unroll
+                        for (int e = 0; e < VW; ++e) { P.v[e] += a.v[e]; E.v[e] += b.v[e]; }
                     }
-                    const int o = 4 * (qoff + q);
-                    const float4 u4 = ld_shared_f4(aux + (cc * AUX + 0) * T + o);
-                    const float4 d4 = ld_shared_f4(aux + (cc * AUX + 1) * T + o);
-                    const float4 z4 = ld_shared_f4(aux + (cc * AUX + 2) * T + o);
-                    const float4 g4 = ld_shared_f4(aux + (cc * AUX + 3) * T + o);
-                    const float uv[4] = {u4.x, u4.y, u4.z, u4.w}, dtv[4] = {d4.x, d4.y, d4.z, d4.w};
-                    const float zv[4] = {z4.x, z4.y, z4.z, z4.w}, gv[4] = {g4.x, g4.y, g4.z, g4.w};
-                    const float Pv[4] = {P.x, P.y, P.z, P.w}, Ev[4] = {E.x, E.y, E.z, E.w};
-                    float duv[4], ddtv[4], dzv[4];
+                    const int o = sbeg + t;
+                    u.ld(aux + (cc * AUX + 0) * T + o);
+                    d.ld(aux + (cc * AUX + 1) * T + o);
+                    z.ld(aux + (cc * AUX + 2) * T + o);
+                    g.ld(aux + (cc * AUX + 3) * T + o);
                     const float dv = dval[it];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
+                    for (int e = 0; e < VW; ++e) {
                         float gu, gz;
-                        const float v = silu_and_grad(uv[e], gu);
-                        const float g = silu_and_grad(zv[e], gz);
-                        const float w = gv[e] * g;
-                        dzv[e] = gv[e] * fmaf(dv, v, Pv[e]) * gz;
-                        ddtv[e] = Ev[e] * v;
-                        duv[e] = fmaf(Ev[e], dtv[e], w * dv) * gu;
-                        if (BULK || 4 * q + e < slen) dacc[it] = fmaf(w, v, dacc[it]);
+                        const float v = silu_and_grad(u.v[e], gu);
+                        const float gg = silu_and_grad(z.v[e], gz);
+                        const float w = g.v[e] * gg;
+                        dz.v[e] = g.v[e] * fmaf(dv, v, P.v[e]) * gz;
+                        ddt.v[e] = E.v[e] * v;
+                        du.v[e] = fmaf(E.v[e], d.v[e], w * dv) * gu;
+                        if (ASYNC || t + e < slen) dacc[it] = fmaf(w, v, dacc[it]);
                     }
                     const long long off = (ch0 + cc) * p.ld_row + t0 + o;
-                    if (BULK) {
-                        *reinterpret_cast<float4*>(p.du + off) = make_float4(duv[0], duv[1], duv[2], duv[3]);
-                        *reinterpret_cast<float4*>(p.ddt + off) = make_float4(ddtv[0], ddtv[1], ddtv[2], ddtv[3]);
-                        *reinterpret_cast<float4*>(p.dz + off) = make_float4(dzv[0], dzv[1], dzv[2], dzv[3]);
+                    if (ASYNC) {
+                        du.st(p.du + off);
+                        ddt.st(p.ddt + off);
+                        dz.st(p.dz + off);
                     } else {
-                        for (int e = 0; e < 4; ++e) {
-                            if (4 * q + e < slen) {
-                                p.du[off + e] = duv[e];
-                                p.ddt[off + e] = ddtv[e];
-                                p.dz[off + e] = dzv[e];
+                        for (int e = 0; e < VW; ++e) {
+                            if (t + e < slen) {
+                                p.du[off + e] = du.v[e];
+                                p.ddt[off + e] = ddt.v[e];
+                                p.dz[off + e] = dz.v[e];
                             }
                         }
                     }
@@ -627,31 +671,37 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uin
             __syncwarp();
         }
 
-        // dtheta leaves the stage
-        if (BULK) {
-            fence_proxy_async();
-            const uint32_t bytes = (uint32_t)tlen * 4u;
+        // dtheta leaves the stage: coalesced 16-byte stores, same piece-to-lane map as the loads
+        if (ASYNC) {
 #pragma unroll
-            for (int k = 0; k < SPT; ++k)
-                if (sc[k].act) bulk_s2g(drowp[k] + t0, th + (k * 32 + lane) * TP, bytes);
-            bulk_commit();
-            // refill the stage used one tile ago: its store must have finished reading
-            if (r >= 1 && r - 1 + STAGES < ntiles) {
-                bulk_wait_read<1>();
-                __syncwarp();
-                issue(ntiles - 1 - (r - 1 + STAGES), (r - 1) % STAGES);
+            for (int i = 0; i < C::NCH_THETA; ++i) {
+                const int id = i * 32 + lane;
+                const int slot = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
+                const int k = slot / 32, w = slot % 32;
+                const bool real_row = (w / NL) < nvalid && ((w % NL) + k * NL) < N;
+                if (real_row && col * 4 < tlen)
+                    *reinterpret_cast<float4*>(dtheta_warp + map.theta_off[i] + t0) =
+                        ld_shared_f4(th + slot * TP + col * 4);
+            }
+            __syncwarp();
+            const int nr = r + STAGES;
+            if (nr < ntiles) {
+                const int nt = ntiles - 1 - nr;
+                map.issue(th, theta_warp, (long long)nt * T, min(T, L - nt * T), lane);
+            } else {
+                cp_async_commit();
             }
         } else {
             for (int cc = 0; cc < nvalid; ++cc)
                 for (int j = 0; j < N; ++j) {
-                    float* dst = p.dtheta + ((ch0 + cc) * N + j) * p.ld_dtheta + t0;
+                    float* dst = dtheta_warp + ((long long)cc * N + j) * p.ld_theta + t0;
                     const float* src = th + slot_of<NL>(cc, j) * TP;
                     for (int t = lane; t < tlen; t += 32) dst[t] = src[t];
                 }
             __syncwarp();
         }
     }
-    if (BULK) bulk_wait_all<0>();
+    if (ASYNC) cp_async_wait<0>();
 
     // ---- per-(channel, state) results ----
 #pragma unroll
@@ -684,44 +734,33 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, uin
             dbr += old.x; dbi += old.y; dcr += old.z; dci += old.w;
         }
         *pb = make_float4(dbr, dbi, dcr, dci);
-        if (p.part_rowsum) p.part_rowsum[o] = rsum[k] + (p.accumulate ? p.part_rowsum[o] : 0.f);
+        if (BIAS && p.part_rowsum) p.part_rowsum[o] = rsum[k] + (p.accumulate ? p.part_rowsum[o] : 0.f);
         if (p.dh0_re) { p.dh0_re[o] = d0r; p.dh0_im[o] = d0i; }
         if (p.h0_re) { p.h0_re[o] = s0r; p.h0_im[o] = s0i; }
     }
     // dD: add the lanes' partial sums channel by channel through the scratch tile
     __syncwarp();
 #pragma unroll
-    for (int it = 0; it < C::ITERS; ++it) {
-        const int idx = lane + 32 * it;
-        if (idx < C::NIDX) pt[idx] = dacc[it];
-    }
+    for (int it = 0; it < C::ITERS; ++it) pt[lane + 32 * it] = dacc[it];
     __syncwarp();
     if (lane < nvalid) {
+        // item idx covers elements [idx*VW, idx*VW+VW) of the CPW*TS block: channel = idx*VW/TS
         float acc = 0.f;
-        for (int q = 0; q < TS / 4; ++q) acc += pt[lane * (TS / 4) + q];
+        for (int idx = 0; idx < 32 * C::ITERS; ++idx)
+            if ((idx * VW) / TS == lane) acc += pt[idx];
         const long long o = ch0 + lane;
         p.part_d[o] = acc + (p.accumulate ? p.part_d[o] : 0.f);
     }
 }
 
-template <class C, bool BULK, bool FAST>
+template <class C, bool ASYNC, bool FAST, bool BIAS>
 __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_bwd_kernel(const ScanBwdParams p) {
     extern __shared__ __align__(128) float smem[];
-    __shared__ uint64_t bars[C::WARPS * C::STAGES];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long ch0 = ((long long)blockIdx.x * C::WARPS + warp) * C::CPW;
     if (ch0 >= p.nch) return;
     const int nvalid = (int)min((long long)C::CPW, (long long)p.nch - ch0);
     float* wsm = smem + (size_t)warp * C::WARP_FLOATS;
-    uint64_t* wbar = bars + warp * C::STAGES;
-    if (BULK) {
-        if (lane == 0) {
-            for (int s = 0; s < C::STAGES; ++s) mbar_init(&wbar[s], 1);
-            fence_mbar_init();
-            fence_proxy_async();
-        }
-        __syncwarp();
-    }
     const int c = lane / C::NL, jl = lane % C::NL;
     const int i = (int)((ch0 + min(c, nvalid - 1)) % p.Dmod);
     StateConsts sc[C::SPT];
@@ -732,7 +771,7 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_bwd_kernel(const S
         const int j = jl + k * C::NL;
         bool okk;
         load_state_consts(sc[k], c < nvalid && j < p.N, j, i, p.N, p.B_r, p.B_theta, p.C_r, p.C_theta,
-                          p.theta_bias, okk);
+                          BIAS ? p.theta_bias : nullptr, okk);
         ccr[k] = sc[k].mr;
         cci[k] = sc[k].mi;
         ok = ok && okk;
@@ -740,9 +779,9 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_bwd_kernel(const S
     if (__all_sync(0xffffffffu, ok)) {
 #pragma unroll
         for (int k = 0; k < C::SPT; ++k) normalise_consts(sc[k], ccr[k], cci[k]);
-        bwd_warp<C, BULK, FAST, true>(p, wsm, wbar, ch0, nvalid, lane, sc, ccr, cci);
+        bwd_warp<C, ASYNC, FAST, true, BIAS>(p, wsm, ch0, nvalid, lane, sc, ccr, cci);
     } else {
-        bwd_warp<C, BULK, FAST, false>(p, wsm, wbar, ch0, nvalid, lane, sc, ccr, cci);
+        bwd_warp<C, ASYNC, FAST, false, BIAS>(p, wsm, ch0, nvalid, lane, sc, ccr, cci);
     }
 }
 
@@ -802,9 +841,9 @@ __global__ void __launch_bounds__(256) reduce_param_grads_kernel(const ReducePar
 // ---------------------------------------------------------------------------
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <class C, bool BULK, bool FAST>
+template <class C, bool ASYNC, bool FAST, bool BIAS>
 cudaError_t launch_fwd_cfg(const ScanFwdParams& p, cudaStream_t stream) {
-    auto kern = scan_unitary_fwd_kernel<C, BULK, FAST>;
+    auto kern = scan_unitary_fwd_kernel<C, ASYNC, FAST, BIAS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const long long tasks = ((long long)p.nch + C::CPW - 1) / C::CPW;
@@ -813,9 +852,9 @@ cudaError_t launch_fwd_cfg(const ScanFwdParams& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-template <class C, bool BULK, bool FAST>
+template <class C, bool ASYNC, bool FAST, bool BIAS>
 cudaError_t launch_bwd_cfg(const ScanBwdParams& p, cudaStream_t stream) {
-    auto kern = scan_unitary_bwd_kernel<C, BULK, FAST>;
+    auto kern = scan_unitary_bwd_kernel<C, ASYNC, FAST, BIAS>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const long long tasks = ((long long)p.nch + C::CPW - 1) / C::CPW;
@@ -824,17 +863,27 @@ cudaError_t launch_bwd_cfg(const ScanBwdParams& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+// Runtime switches -> template parameters.  The plain (unaligned) path and the
+// special-function trigonometry are fallback / measurement variants and are
+// instantiated with the phase offset always on, to keep the build small.
 template <class C>
-cudaError_t launch_fwd_sel(const ScanFwdParams& p, bool bulk, bool fast, cudaStream_t s) {
-    if (bulk) return fast ? launch_fwd_cfg<C, true, true>(p, s) : launch_fwd_cfg<C, true, false>(p, s);
-    return fast ? launch_fwd_cfg<C, false, true>(p, s) : launch_fwd_cfg<C, false, false>(p, s);
+cudaError_t launch_fwd_sel(const ScanFwdParams& p, bool async, bool fast, cudaStream_t s) {
+    const bool bias = p.theta_bias != nullptr;
+    if (!async) return launch_fwd_cfg<C, false, false, true>(p, s);
+    if (fast) return launch_fwd_cfg<C, true, true, true>(p, s);
+    return bias ? launch_fwd_cfg<C, true, false, true>(p, s) : launch_fwd_cfg<C, true, false, false>(p, s);
 }
 
 template <class C>
-cudaError_t launch_bwd_sel(const ScanBwdParams& p, bool bulk, bool fast, cudaStream_t s) {
-    if (bulk) return fast ? launch_bwd_cfg<C, true, true>(p, s) : launch_bwd_cfg<C, true, false>(p, s);
-    return fast ? launch_bwd_cfg<C, false, true>(p, s) : launch_bwd_cfg<C, false, false>(p, s);
+cudaError_t launch_bwd_sel(const ScanBwdParams& p, bool async, bool fast, cudaStream_t s) {
+    const bool bias = p.theta_bias != nullptr || p.part_rowsum != nullptr;
+    if (!async) return launch_bwd_cfg<C, false, false, true>(p, s);
+    if (fast) return launch_bwd_cfg<C, true, true, true>(p, s);
+    return bias ? launch_bwd_cfg<C, true, false, true>(p, s) : launch_bwd_cfg<C, true, false, false>(p, s);
 }
+
+// a warp's rows must be addressable with 32-bit float offsets from its first row
+inline bool offsets_fit(long long ld, int rows_per_warp) { return ld * (long long)rows_per_warp < (1LL << 31); }
 
 }  // namespace
 
@@ -846,22 +895,22 @@ cudaError_t launch_scan_unitary_fwd(const ScanFwdParams& p_, cudaStream_t stream
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
     const ScanOptions& o = scan_options();
-    const bool bulk = !o.force_plain && (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) &&
-                      aligned16(p.theta) && aligned16(p.u) && aligned16(p.dt) && aligned16(p.z) &&
-                      (p.y == nullptr || aligned16(p.y));
+    const bool async = !o.force_plain && (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) &&
+                       aligned16(p.theta) && aligned16(p.u) && aligned16(p.dt) && aligned16(p.z) &&
+                       (p.y == nullptr || aligned16(p.y)) && offsets_fit(p.ld_theta, 128);
     const bool fast = o.fast_trig != 0;
     const int N = p.N;
-    if (N <= 4) return launch_fwd_sel<FwdCfg<4, 1, 32, 3, 4>>(p, bulk, fast, stream);
-    if (N <= 8) return launch_fwd_sel<FwdCfg<8, 1, 64, 3, 3>>(p, bulk, fast, stream);
+    if (N <= 4) return launch_fwd_sel<FwdCfg<4, 1, 32, 2, 4>>(p, async, fast, stream);
+    if (N <= 8) return launch_fwd_sel<FwdCfg<8, 1, 32, 2, 4>>(p, async, fast, stream);
     if (N <= 16) {
-        if (o.variant == 1) return launch_fwd_sel<FwdCfg<8, 2, 64, 3, 3>>(p, bulk, fast, stream);
-        if (o.variant == 2) return launch_fwd_sel<FwdCfg<16, 1, 128, 3, 3>>(p, bulk, fast, stream);
-        if (o.variant == 3) return launch_fwd_sel<FwdCfg<16, 1, 32, 4, 5>>(p, bulk, fast, stream);
-        return launch_fwd_sel<FwdCfg<16, 1, 64, 3, 3>>(p, bulk, fast, stream);
+        if (o.variant == 1) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 4>>(p, async, fast, stream);
+        if (o.variant == 2) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 4>>(p, async, fast, stream);
+        if (o.variant == 3) return launch_fwd_sel<FwdCfg<16, 1, 32, 3, 4>>(p, async, fast, stream);
+        return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 4>>(p, async, fast, stream);
     }
-    if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 64, 3, 3>>(p, bulk, fast, stream);
-    if (N <= 64) return launch_fwd_sel<FwdCfg<32, 2, 32, 3, 3>>(p, bulk, fast, stream);
-    if (N <= 128) return launch_fwd_sel<FwdCfg<32, 4, 32, 3, 2>>(p, bulk, fast, stream);
+    if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 32, 2, 4>>(p, async, fast, stream);
+    if (N <= 64) return launch_fwd_sel<FwdCfg<32, 2, 32, 2, 4>>(p, async, fast, stream);
+    if (N <= 128) return launch_fwd_sel<FwdCfg<32, 4, 32, 2, 2>>(p, async, fast, stream);
     return cudaErrorInvalidValue;
 }
 
@@ -870,24 +919,25 @@ cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p_, cudaStream_t stream
     ScanBwdParams p = p_;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
+    if (p.ld_dtheta != p.ld_theta) return cudaErrorInvalidValue;
     const ScanOptions& o = scan_options();
-    const bool bulk = !o.force_plain && (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_dtheta % 4 == 0) &&
-                      (p.ld_row % 4 == 0) && aligned16(p.theta) && aligned16(p.dtheta) && aligned16(p.u) &&
-                      aligned16(p.dt) && aligned16(p.z) && aligned16(p.gy) && aligned16(p.du) &&
-                      aligned16(p.ddt) && aligned16(p.dz);
+    const bool async = !o.force_plain && (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) &&
+                       aligned16(p.theta) && aligned16(p.dtheta) && aligned16(p.u) && aligned16(p.dt) &&
+                       aligned16(p.z) && aligned16(p.gy) && aligned16(p.du) && aligned16(p.ddt) &&
+                       aligned16(p.dz) && offsets_fit(p.ld_theta, 128);
     const bool fast = o.fast_trig != 0;
     const int N = p.N;
-    if (N <= 4) return launch_bwd_sel<BwdCfg<4, 1, 32, 32, 3, 3>>(p, bulk, fast, stream);
-    if (N <= 8) return launch_bwd_sel<BwdCfg<8, 1, 64, 32, 3, 2>>(p, bulk, fast, stream);
+    if (N <= 4) return launch_bwd_sel<BwdCfg<4, 1, 32, 32, 2, 2>>(p, async, fast, stream);
+    if (N <= 8) return launch_bwd_sel<BwdCfg<8, 1, 32, 32, 2, 2>>(p, async, fast, stream);
     if (N <= 16) {
-        if (o.variant == 1) return launch_bwd_sel<BwdCfg<8, 2, 64, 32, 3, 3>>(p, bulk, fast, stream);
-        if (o.variant == 2) return launch_bwd_sel<BwdCfg<16, 1, 128, 32, 3, 3>>(p, bulk, fast, stream);
-        if (o.variant == 3) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 4, 3>>(p, bulk, fast, stream);
-        return launch_bwd_sel<BwdCfg<16, 1, 64, 32, 3, 5>>(p, bulk, fast, stream);
+        if (o.variant == 1) return launch_bwd_sel<BwdCfg<8, 2, 32, 32, 2, 2>>(p, async, fast, stream);
+        if (o.variant == 2) return launch_bwd_sel<BwdCfg<16, 1, 64, 32, 2, 2>>(p, async, fast, stream);
+        if (o.variant == 3) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 3, 2>>(p, async, fast, stream);
+        return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 2>>(p, async, fast, stream);
     }
-    if (N <= 32) return launch_bwd_sel<BwdCfg<32, 1, 64, 32, 3, 5>>(p, bulk, fast, stream);
-    if (N <= 64) return launch_bwd_sel<BwdCfg<32, 2, 32, 32, 3, 4>>(p, bulk, fast, stream);
-    if (N <= 128) return launch_bwd_sel<BwdCfg<32, 4, 32, 32, 3, 2>>(p, bulk, fast, stream);
+    if (N <= 32) return launch_bwd_sel<BwdCfg<32, 1, 32, 32, 2, 2>>(p, async, fast, stream);
+    if (N <= 64) return launch_bwd_sel<BwdCfg<32, 2, 32, 32, 2, 2>>(p, async, fast, stream);
+    if (N <= 128) return launch_bwd_sel<BwdCfg<32, 4, 32, 32, 2, 2>>(p, async, fast, stream);
     return cudaErrorInvalidValue;
 }
 
