@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaussm_b200.so")
-SOURCES = ["scan_unitary.cu", "projection.cu", "api.cu"]
+SOURCES = ["scan_unitary.cu", "projection.cu", "api.cu", "noalloc.cu"]
 HEADERS = ["common.cuh", "scan_unitary.cuh", "projection.cuh", os.path.join("..", "..", "include", "aussm_b200.h")]
 
 

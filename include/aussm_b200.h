@@ -81,6 +81,37 @@ int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const 
                                 float* dh0_re, float* dh0_im, int B, int D, int N, int L, void* workspace,
                                 size_t workspace_bytes, aussm_stream_t stream);
 
+/* Backward scan for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference (whose host functions allocate their outputs
+ * and temporaries through torch on every call).
+ *
+ * Same arguments and results as aussm_b200_scan_unitary_bwd, minus the
+ * workspace: the scratch for the per-channel partial sums is a fixed array of
+ * AUSSM_STATIC_SCRATCH_BYTES inside the library image.  It is meant for code
+ * that runs where cudaMalloc or a framework allocator is off limits - inside a
+ * serving loop that must not synchronise the device, in a plug-in that is
+ * handed nothing but its input and output buffers, under a fixed memory plan -
+ * and it calls no cudaMalloc, cudaFree or allocating library routine.
+ *
+ *  - Limit: B*D*(5*N+1)*4 bytes <= AUSSM_STATIC_SCRATCH_BYTES, otherwise
+ *    AUSSM_EWORKSPACE is returned and nothing is launched.
+ *  - Cost: every GPU on which this library is loaded holds the array until the
+ *    process exits, whether or not this function is ever called.
+ *  - The first call on a device looks up the array's device address (no
+ *    allocation); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array.  Each call overwrites every
+ *    word it later reads, so earlier contents never matter, but two calls whose
+ *    kernels overlap on the GPU (different streams) race on it: serialise them. */
+#define AUSSM_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int aussm_b200_scan_unitary_bwd_static(const float* grad_y, const float* gh1_re, const float* gh1_im,
+                                       const float* theta, const float* u, const float* dt, const float* z,
+                                       const float* B_r, const float* B_theta, const float* C_r,
+                                       const float* C_theta, const float* Dskip, const float* h1_re,
+                                       const float* h1_im, float* dtheta, float* du, float* ddt, float* dz,
+                                       float* dB_r, float* dB_theta, float* dC_r, float* dC_theta, float* dD,
+                                       float* dh0_re, float* dh0_im, int B, int D, int N, int L,
+                                       aussm_stream_t stream);
+
 /* ---- drop-in operators ---------------------------------------------------
  * aussm_b200_unitary_fwd replaces ssm_adaptive_cuda_forward_unitary
  * (ssm_adaptive_unitary_forward.cu:191-277, schema :284) and
