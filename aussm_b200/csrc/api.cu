@@ -10,6 +10,7 @@
 #include <string>
 
 #include "../../include/aussm_b200.h"
+#include "gemm_tf32x3.cuh"
 #include "projection.cuh"
 #include "scan_unitary.cuh"
 
@@ -59,7 +60,7 @@ struct Plan {
     long long rows;      // B*D*N
     int window;          // steps per window
     long long ldw;       // row pitch of the window (floats)
-    size_t off_theta, off_h, off_gh, off_part, total;   // byte offsets
+    size_t off_theta, off_h, off_gh, off_part, off_proj, total;   // byte offsets
 };
 
 Plan make_plan(int B, int D, int N, int L) {
@@ -86,6 +87,8 @@ Plan make_plan(int B, int D, int N, int L) {
     off = align_up(off + (size_t)p.rows * 2 * 4, 256);
     p.off_part = off;
     off = align_up(off + scan_bwd_partial_floats((long long)B * D, N) * 4, 256);
+    p.off_proj = off;    // TF32 hi/lo parts of x, of the u window and of the dtheta window
+    off = align_up(off + proj_scratch_floats(B, D, N, p.ldw) * 4, 256);
     p.total = off;
     return p;
 }
@@ -98,7 +101,7 @@ struct OpArgs {
 // Forward over all windows.  y == nullptr: state only.  The final state goes
 // to (out_re, out_im), which may be the workspace pair itself.
 int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, float* y, float* out_re,
-                    float* out_im, char* ws, const Plan& pl, cudaStream_t stream) {
+                    float* out_im, char* ws, const Plan& pl, ProjScratch& ps, cudaStream_t stream) {
     float* theta_w = reinterpret_cast<float*>(ws + pl.off_theta);
     float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
     float* cur_im = cur_re + pl.rows;
@@ -107,7 +110,7 @@ int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, flo
         const long long t0 = (long long)w * pl.window;
         const int tl = (int)std::min<long long>(pl.window, a.L - t0);
         const ProjDims pd = {a.B, a.D, a.N, a.L, pl.ldw, t0, tl};
-        if (int rc = proj_theta(pd, a.x, a.u, theta_w, stream)) return rc;
+        if (int rc = proj_theta(pd, a.x, a.u, theta_w, ps, stream)) return rc;
         const bool last = (w == nwin - 1);
         ScanFwdParams sp = {};
         sp.theta = theta_w;
@@ -156,6 +159,7 @@ int aussm_b200_set_option(const char* name, int value) {
     else if (!strcmp(name, "force_plain")) o.force_plain = value;
     else if (!strcmp(name, "variant")) o.variant = value;
     else if (!strcmp(name, "gemm_tile")) g_window_override = value;
+    else if (!strcmp(name, "gemm_backend")) set_gemm_backend(value);
     else {
         set_error("unknown option '%s'", name);
         return AUSSM_EINVAL;
@@ -238,6 +242,43 @@ int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const 
     return AUSSM_OK;
 }
 
+size_t aussm_b200_gemm_tf32x3_workspace_bytes(int M, int N, int K, int batches, int a_batched, int b_batched) {
+    if (M <= 0 || N <= 0 || K <= 0 || batches <= 0) return 0;
+    const size_t na = (size_t)M * K * (a_batched ? batches : 1), nb = (size_t)N * K * (b_batched ? batches : 1);
+    return align_up(2 * (na + nb) * sizeof(float) + 1024, 256);
+}
+
+int aussm_b200_gemm_tf32x3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
+                           int b_batched, float* C, int M, int N, int K, int batches, int reduce_batches, int beta,
+                           void* workspace, size_t workspace_bytes, aussm_stream_t stream_) {
+    if (!A || !Bm || !C || M <= 0 || N <= 0 || K <= 0 || batches <= 0) {
+        set_error("gemm_tf32x3: null pointer or non-positive size");
+        return AUSSM_EINVAL;
+    }
+    const size_t need = aussm_b200_gemm_tf32x3_workspace_bytes(M, N, K, batches, a_batched, b_batched);
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) {
+        set_error("gemm_tf32x3: workspace of %zu bytes (256-byte aligned) required, got %zu", need, workspace_bytes);
+        return AUSSM_EWORKSPACE;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
+    // packed operands: K-major = (rows, K) with K contiguous; MN-major = (K, rows) with rows contiguous
+    const long long a_rows = a_mn_major ? K : M, a_cols = a_mn_major ? M : K;
+    const long long b_rows = b_mn_major ? K : N, b_cols = b_mn_major ? N : K;
+    const int na = a_batched ? batches : 1, nb = b_batched ? batches : 1;
+    float* a_hi = static_cast<float*>(workspace);
+    float* a_lo = a_hi + (size_t)a_rows * a_cols * na;
+    float* b_hi = a_lo + (size_t)a_rows * a_cols * na;
+    float* b_lo = b_hi + (size_t)b_rows * b_cols * nb;
+    if (int rc = split_tf32(A, a_cols, a_rows * a_cols, a_hi, a_lo, a_cols, a_rows * a_cols, a_rows, a_cols, na, stream))
+        return rc;
+    if (int rc = split_tf32(Bm, b_cols, b_rows * b_cols, b_hi, b_lo, b_cols, b_rows * b_cols, b_rows, b_cols, nb, stream))
+        return rc;
+    const SplitOperand sa = {a_hi, a_lo, a_mn_major, a_cols, a_batched ? a_rows * a_cols : 0};
+    const SplitOperand sb = {b_hi, b_lo, b_mn_major, b_cols, b_batched ? b_rows * b_cols : 0};
+    const GemmShape shape = {M, N, K, batches, reduce_batches, beta, N, reduce_batches ? 0 : (long long)M * N};
+    return gemm_tf32x3(sa, sb, C, shape, stream);
+}
+
 size_t aussm_b200_unitary_workspace_bytes(int B, int D, int N, int L) {
     if (B <= 0 || D <= 0 || N <= 0 || L <= 0) return 0;
     return make_plan(B, D, N, L).total;
@@ -266,7 +307,10 @@ int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, cons
     char* ws = static_cast<char*>(workspace);
     float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
     const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
-    return run_unitary_fwd(a, h0_re, h0_im, y, h1_re ? h1_re : cur_re, h1_im ? h1_im : cur_re + pl.rows, ws, pl,
+    ProjScratch ps;
+    proj_scratch_bind(ps, reinterpret_cast<float*>(ws + pl.off_proj), B, D, N, pl.ldw);
+    if (int rc = proj_begin(B, D, N, L, pl.ldw, x, u, ps, (cudaStream_t)stream)) return rc;
+    return run_unitary_fwd(a, h0_re, h0_im, y, h1_re ? h1_re : cur_re, h1_im ? h1_im : cur_re + pl.rows, ws, pl, ps,
                            (cudaStream_t)stream);
 }
 
@@ -307,12 +351,15 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
     float* part_d = part_bc + nch * N * 4;
     float* part_rowsum = part_d + nch;
     const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
+    ProjScratch ps;
+    proj_scratch_bind(ps, reinterpret_cast<float*>(ws + pl.off_proj), B, D, N, pl.ldw);
+    if (int rc = proj_begin(B, D, N, L, pl.ldw, x, u, ps, stream)) return rc;
 
     // final state: given by the caller, or recomputed by a state-only forward sweep
     const float* hend_re = h1_re;
     const float* hend_im = h1_im;
     if (!h1_re) {
-        if (int rc = run_unitary_fwd(a, h0_re, h0_im, nullptr, cur_re, cur_im, ws, pl, stream)) return rc;
+        if (int rc = run_unitary_fwd(a, h0_re, h0_im, nullptr, cur_re, cur_im, ws, pl, ps, stream)) return rc;
         hend_re = cur_re;
         hend_im = cur_im;
     }
@@ -324,7 +371,7 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
         const bool first = (w == nwin - 1);   // first processed = last in time
         const bool final_ = (w == 0);
         const ProjDims pd = {B, D, N, L, pl.ldw, t0, tl};
-        if (int rc = proj_theta(pd, x, u, theta_w, stream)) return rc;
+        if (int rc = proj_theta(pd, x, u, theta_w, ps, stream)) return rc;
         ScanBwdParams p = {};
         p.theta = theta_w; p.theta_bias = x_bias;
         p.u = u + t0; p.dt = dt + t0; p.z = z + t0; p.gy = grad_y + t0;
@@ -345,8 +392,7 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
         p.ld_theta = pl.ldw; p.ld_dtheta = pl.ldw; p.ld_row = L;
         cudaError_t e = launch_scan_unitary_bwd(p, stream);
         if (e != cudaSuccess) return cuda_fail(e, "unitary scan backward launch");
-        if (int rc = proj_dx(pd, theta_w, u, dx, first, stream)) return rc;
-        if (int rc = proj_du(pd, theta_w, x, du, stream)) return rc;
+        if (int rc = proj_adjoints(pd, theta_w, x, u, dx, du, first, ps, stream)) return rc;
     }
     ReduceParams r = {};
     r.part_bc = part_bc; r.part_d = part_d; r.part_rowsum = part_rowsum;

@@ -1,0 +1,480 @@
+// tcgen05 / TMEM / TMA implementation of the float32-accurate GEMM used by the
+// phase projection theta = x u and its two adjoints (replaces the d^2 inner
+// loops of csrc/cuda/ssm_adaptive_unitary_forward.cu:83-110 and the atomics of
+// ssm_adaptive_unitary_backward.cu:419-490 of the reference).
+//
+// One CTA computes a 128 x 128 tile of C.  Roles: warp 0 = TMA producer (one
+// lane), warp 1 = MMA issuer (one lane; the warp also owns the TMEM
+// allocation), warps 2-9 = accumulate/epilogue (TMEM -> registers -> global).
+// Operands arrive pre-split into TF32 hi/lo parts; per 32-deep K block the
+// issuer runs 4 (K=8 steps) x 3 (hi*hi, hi*lo, lo*hi) tcgen05.mma instructions
+// into float32 accumulators of 128 lanes x 128 columns in tensor memory.
+//
+// Shared-memory operand tiles use the swizzles the TMA engine writes and the
+// MMA descriptors expect.  K-major operand (K contiguous in memory): 128-byte
+// swizzle, rows of 32 floats, 8-row groups 1024 B apart.  MN-major operand
+// (row index contiguous): "128-byte swizzle with 32-byte atom" (the only
+// layout 32-bit MN-major operands have), TMA boxes of 32 K-rows x 32
+// row-elements (4 KB) placed 4096 B apart along the row index, groups of four
+// K-rows 512 B apart inside a box.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records the reason
+// in the device status word, and the CTA still frees its tensor memory.
+#include "gemm_tf32x3.cuh"
+
+#include <cuda.h>
+#include <stdint.h>
+
+#include <mutex>
+
+#include "../../include/aussm_b200.h"
+#include "common.cuh"
+#include "projection.cuh"
+#include "scan_unitary.cuh"
+
+namespace aussm {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32;          // BK floats = 128 bytes = one swizzle row
+constexpr int STAGES = 3;
+constexpr int A_TILE_BYTES = BM * BK * 4;            // 16 KB
+constexpr int B_TILE_BYTES = BN * BK * 4;            // 16 KB
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // hi + lo of both operands: 64 KB
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + slack for 1024-byte alignment
+// Tensor-memory accumulation truncates instead of rounding, so a long K loop drifts (measured 3.5e-5 relative
+// at K = 4096).  The K loop is therefore cut into chunks of CHUNK_KB blocks: each chunk accumulates from zero
+// into one of two TMEM buffers and the epilogue warps add the finished chunk into float32 registers
+// (round-to-nearest) while the next chunk runs.  Each buffer holds two accumulators: the hi*hi products and the
+// two small cross terms, so that adding the tiny terms does not cost the big sum an extra truncation.
+constexpr int CHUNK_KB = 2;
+constexpr int ACC_COLS = 2 * BN;                     // main + cross accumulator of one buffer
+constexpr int TMEM_COLS = 2 * ACC_COLS;              // 512: two buffers
+constexpr int EPI_WARPS = 8;                         // two per TMEM lane quarter, 64 columns each
+constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
+
+struct GemmKernelParams {
+    float* C;
+    long long ldc;
+    long long c_batch_stride;
+    int M, N, K;
+    int kbatches;      // batch entries summed inside the K loop (1 when batches are independent)
+    int a_batched;     // 0: operand shared by all batch entries (batch coordinate 0)
+    int b_batched;
+    int beta;
+    int* status;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_addr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c0), "r"(c1),
+        "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(smem_holder)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+// arrives on the mbarrier when all MMAs issued so far by this thread have completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptors (64 bit): start address >> 4 in bits 0-13,
+// leading byte offset >> 4 in bits 16-29, stride byte offset >> 4 in bits
+// 32-45, descriptor version 1 in bits 46-47, 128-byte swizzle (2) in bits 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint64_t layout_type) {
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (layout_type << 61);
+}
+
+// descriptor of the kk-th K=8 slice of an operand tile
+template <int MN_MAJOR>
+__device__ __forceinline__ uint64_t operand_desc(uint32_t tile_saddr, int kk) {
+    if (MN_MAJOR) {
+        // 32-bit MN-major operands only exist in the "128-byte swizzle, 32-byte atom" layout (type 1): boxes of
+        // 32 K-rows x 128 B placed 4096 B apart along the row index, groups of 4 K-rows 512 B apart; a K=8
+        // slice is two such groups, 1024 B further per step
+        return smem_desc(tile_saddr + kk * 1024, 4096, 512, 1);
+    }
+    // 128-byte swizzle (type 2): rows of 128 B (32 floats of K), 8-row groups 1024 B apart; a K=8 slice
+    // starts 32 B further into the row
+    return smem_desc(tile_saddr + kk * 32, 16, 1024, 2);
+}
+
+// Instruction descriptor for kind::tf32, float32 accumulate: c_format=1 (bits 4-5), a/b format TF32=2
+// (bits 7-9, 10-12), a/b major (bits 15, 16), N>>3 (bits 17-22), M>>4 (bits 24-28).
+template <int A_MN, int B_MN>
+__device__ __forceinline__ constexpr uint32_t instr_desc() {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)A_MN << 15) | ((uint32_t)B_MN << 16) |
+           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
+                   const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
+                   const GemmKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ int failed;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int zb = blockIdx.z;                                  // independent batch entry (0 when reducing)
+    const int kblocks = (p.K + BK - 1) / BK;
+    const int total = kblocks * p.kbatches;
+    const int nchunks = (total + CHUNK_KB - 1) / CHUNK_KB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], EPI_WARPS);
+        }
+        failed = 0;
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc(&tmem_holder, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            for (int it = 0; it < total; ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, p.status)) { failed = 1; break; }
+                const int kb = it % kblocks;
+                const int batch = p.kbatches > 1 ? it / kblocks : zb;
+                const int ba = p.a_batched ? batch : 0, bb = p.b_batched ? batch : 0;
+                uint8_t* st = smem + s * STAGE_BYTES;
+                uint8_t* a_hi = st;
+                uint8_t* a_lo = st + A_TILE_BYTES;
+                uint8_t* b_hi = st + 2 * A_TILE_BYTES;
+                uint8_t* b_lo = st + 2 * A_TILE_BYTES + B_TILE_BYTES;
+                mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
+                const int k0 = kb * BK;
+                if (A_MN) {
+#pragma unroll
+                    for (int i = 0; i < BM / 32; ++i) {
+                        tma_load_3d(a_hi + i * 4096, &mapA_hi, &full_bar[s], m0 + 32 * i, k0, ba);
+                        tma_load_3d(a_lo + i * 4096, &mapA_lo, &full_bar[s], m0 + 32 * i, k0, ba);
+                    }
+                } else {
+                    tma_load_3d(a_hi, &mapA_hi, &full_bar[s], k0, m0, ba);
+                    tma_load_3d(a_lo, &mapA_lo, &full_bar[s], k0, m0, ba);
+                }
+                if (B_MN) {
+#pragma unroll
+                    for (int i = 0; i < BN / 32; ++i) {
+                        tma_load_3d(b_hi + i * 4096, &mapB_hi, &full_bar[s], n0 + 32 * i, k0, bb);
+                        tma_load_3d(b_lo + i * 4096, &mapB_lo, &full_bar[s], n0 + 32 * i, k0, bb);
+                    }
+                } else {
+                    tma_load_3d(b_hi, &mapB_hi, &full_bar[s], k0, n0, bb);
+                    tma_load_3d(b_lo, &mapB_lo, &full_bar[s], k0, n0, bb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer: one chunk of CHUNK_KB K-blocks per TMEM buffer ----
+            constexpr uint32_t idesc = instr_desc<A_MN, B_MN>();
+            bool ok = true;
+            int it = 0;
+            for (int c = 0; c < nchunks && ok; ++c) {
+                const int buf = c & 1;
+                const uint32_t aph = (uint32_t)(c >> 1) & 1u;
+                if (!mbar_wait_bounded(&acc_empty[buf], aph ^ 1u, p.status)) { failed = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t acc_main = tmem_base + (uint32_t)(buf * ACC_COLS);
+                const uint32_t acc_cross = acc_main + BN;
+                for (int j = 0; j < CHUNK_KB && it < total; ++j, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait_bounded(&full_bar[s], ph, p.status)) { failed = 1; ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_addr(smem + s * STAGE_BYTES);
+                    const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES, b_hi = st + 2 * A_TILE_BYTES,
+                                   b_lo = st + 2 * A_TILE_BYTES + B_TILE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < BK / 8; ++kk) {
+                        const uint64_t ah = operand_desc<A_MN>(a_hi, kk), al = operand_desc<A_MN>(a_lo, kk);
+                        const uint64_t bh = operand_desc<B_MN>(b_hi, kk), bl = operand_desc<B_MN>(b_lo, kk);
+                        const uint32_t first = (j > 0 || kk > 0) ? 1u : 0u;
+                        umma_tf32(acc_main, ah, bh, idesc, first);
+                        umma_tf32(acc_cross, ah, bl, idesc, first);
+                        umma_tf32(acc_cross, al, bh, idesc, 1u);
+                    }
+                    umma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
+                }
+                umma_commit(&acc_full[buf]);         // chunk complete (arrives even after a failed wait)
+            }
+        }
+    } else {
+        // ---- accumulate + epilogue: warps 2..9; TMEM lane quarter = warp % 4, column half = (warp - 2) / 4 ----
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        bool ok = true;
+        for (int c = 0; c < nchunks && ok; ++c) {
+            const int buf = c & 1;
+            const uint32_t aph = (uint32_t)(c >> 1) & 1u;
+            ok = mbar_wait_bounded(&acc_full[buf], aph, p.status);
+            tc_fence_after();
+            if (ok) {
+                const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * ACC_COLS + half * 64);
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    float vm[32], vc[32];
+                    tmem_ld32(t0 + part * 32, vm);            // hi*hi
+                    tmem_ld32(t0 + BN + part * 32, vc);       // hi*lo + lo*hi
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[part * 32 + i] += vm[i] + vc[i];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);      // the issuer may overwrite this buffer
+        }
+        if (ok && !failed) {
+            const int row = m0 + quarter * 32 + lane;
+            if (row < p.M) {
+                const int col0 = n0 + half * 64;
+                float* crow = p.C + (long long)zb * p.c_batch_stride + (long long)row * p.ldc + col0;
+#pragma unroll
+                for (int g = 0; g < 16; ++g) {
+                    const int col = col0 + 4 * g;
+                    float* dst = crow + 4 * g;
+                    if (col + 3 < p.N) {
+                        float4 o = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
+                        if (p.beta) {
+                            const float4 cin = *reinterpret_cast<const float4*>(dst);
+                            o.x += cin.x; o.y += cin.y; o.z += cin.z; o.w += cin.w;
+                        }
+                        *reinterpret_cast<float4*>(dst) = o;
+                    } else {
+                        for (int e = 0; e < 4; ++e)
+                            if (col + e < p.N) dst[e] = acc[4 * g + e] + (p.beta ? dst[e] : 0.f);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---- hi/lo split ----------------------------------------------------------
+__device__ __forceinline__ float to_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ src, long long ld_src,
+                                                         long long src_bs, float* __restrict__ hi,
+                                                         float* __restrict__ lo, long long ld_dst, long long dst_bs,
+                                                         long long rows, long long cols4) {
+    const long long b = blockIdx.z;
+    const long long total = rows * cols4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols4, c = (i % cols4) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(src + b * src_bs + r * ld_src + c);
+        float4 h, l;
+        h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
+        l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y); l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
+        *reinterpret_cast<float4*>(hi + b * dst_bs + r * ld_dst + c) = h;
+        *reinterpret_cast<float4*>(lo + b * dst_bs + r * ld_dst + c) = l;
+    }
+}
+
+// ---- host side --------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// Tensor map of one split part: K-major -> dims (K, rows, batch), box (32, box_rows, 1);
+// MN-major -> dims (rows, K, batch), box (32, 32, 1).  Out-of-range elements read as zero.
+int make_map(CUtensorMap* map, const float* base, int mn_major, long long rows, long long K, long long ld,
+             long long batch_stride, int batches, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return AUSSM_ECUDA;
+    }
+    cuuint64_t dims[3], strides[2];
+    cuuint32_t box[3], estr[3] = {1, 1, 1};
+    if (mn_major) {
+        dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K;
+        box[0] = 32; box[1] = 32;
+    } else {
+        dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows;
+        box[0] = 32; box[1] = (cuuint32_t)box_rows;
+    }
+    dims[2] = (cuuint64_t)batches;
+    box[2] = 1;
+    strides[0] = (cuuint64_t)ld * 4;
+    strides[1] = (cuuint64_t)(batches > 1 ? batch_stride : (long long)dims[1] * ld) * 4;
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with code %d (rows=%lld K=%lld ld=%lld batches=%d mn_major=%d)", (int)r,
+                  rows, K, ld, batches, mn_major);
+        return AUSSM_ECUDA;
+    }
+    return AUSSM_OK;
+}
+
+template <int A_MN, int B_MN>
+int launch(const CUtensorMap* maps, const GemmKernelParams& kp, dim3 grid, cudaStream_t stream) {
+    auto kern = gemm_tf32x3_kernel<A_MN, B_MN>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) {
+        set_error("gemm_tf32x3: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        return AUSSM_ECUDA;
+    }
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("gemm_tf32x3 launch: %s", cudaGetErrorString(e));
+        return AUSSM_ECUDA;
+    }
+    return AUSSM_OK;
+}
+
+bool ok16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+bool gemm_tf32x3_supported(const SplitOperand& A, const SplitOperand& B, const float* C, const GemmShape& s) {
+    if (s.M <= 0 || s.N <= 0 || s.K <= 0 || s.batches <= 0) return false;
+    if (A.ld % 4 || B.ld % 4 || s.ldc % 4 || A.batch_stride % 4 || B.batch_stride % 4 || s.c_batch_stride % 4)
+        return false;
+    if (!ok16(A.hi) || !ok16(A.lo) || !ok16(B.hi) || !ok16(B.lo) || !ok16(C)) return false;
+    return encode_fn() != nullptr;
+}
+
+int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const GemmShape& s, cudaStream_t stream) {
+    if (!gemm_tf32x3_supported(A, B, C, s)) {
+        set_error("gemm_tf32x3: unsupported shape or alignment (M=%d N=%d K=%d)", s.M, s.N, s.K);
+        return AUSSM_EINVAL;
+    }
+    alignas(64) CUtensorMap maps[4];
+    const int ab = A.batch_stride != 0 ? s.batches : 1, bb = B.batch_stride != 0 ? s.batches : 1;
+    if (int rc = make_map(&maps[0], A.hi, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
+    if (int rc = make_map(&maps[1], A.lo, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
+    if (int rc = make_map(&maps[2], B.hi, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
+    if (int rc = make_map(&maps[3], B.lo, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
+    GemmKernelParams kp;
+    kp.C = C; kp.ldc = s.ldc; kp.c_batch_stride = s.c_batch_stride;
+    kp.M = s.M; kp.N = s.N; kp.K = s.K;
+    kp.kbatches = s.reduce_batches ? s.batches : 1;
+    kp.beta = s.beta;
+    kp.a_batched = A.batch_stride != 0;
+    kp.b_batched = B.batch_stride != 0;
+    kp.status = device_status_ptr();
+    if (!kp.status) {
+        set_error("gemm_tf32x3: device status word unavailable");
+        return AUSSM_ECUDA;
+    }
+    dim3 grid((s.M + BM - 1) / BM, (s.N + BN - 1) / BN, s.reduce_batches ? 1 : s.batches);
+    if (A.mn_major) return B.mn_major ? launch<1, 1>(maps, kp, grid, stream) : launch<1, 0>(maps, kp, grid, stream);
+    return B.mn_major ? launch<0, 1>(maps, kp, grid, stream) : launch<0, 0>(maps, kp, grid, stream);
+}
+
+int split_tf32(const float* src, long long ld_src, long long src_batch_stride, float* hi, float* lo, long long ld_dst,
+               long long dst_batch_stride, long long rows, long long cols, int batches, cudaStream_t stream) {
+    if (cols % 4 || ld_src % 4 || ld_dst % 4 || !ok16(src) || !ok16(hi) || !ok16(lo)) {
+        set_error("split_tf32: rows must be 16-byte aligned (cols=%lld ld_src=%lld ld_dst=%lld)", cols, ld_src, ld_dst);
+        return AUSSM_EINVAL;
+    }
+    const long long total = rows * (cols / 4);
+    if (total <= 0 || batches <= 0) return AUSSM_OK;
+    const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148 * 16);
+    split_tf32_kernel<<<dim3(blocks, 1, batches), 256, 0, stream>>>(src, ld_src, src_batch_stride, hi, lo, ld_dst,
+                                                                    dst_batch_stride, rows, cols / 4);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("split_tf32 launch: %s", cudaGetErrorString(e));
+        return AUSSM_ECUDA;
+    }
+    return AUSSM_OK;
+}
+
+}  // namespace aussm

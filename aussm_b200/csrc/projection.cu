@@ -1,11 +1,14 @@
-// Library-GEMM implementation of the phase projection and its adjoints.
+// Phase projection and its adjoints: tcgen05 three-term TF32 GEMMs, with the
+// library SGEMM as the fallback for shapes the TMA path cannot address.
 #include "projection.cuh"
 
 #include <cublas_v2.h>
+#include <stdint.h>
 
 #include <mutex>
 
 #include "../../include/aussm_b200.h"
+#include "gemm_tf32x3.cuh"
 
 namespace aussm {
 
@@ -14,6 +17,7 @@ namespace {
 constexpr int kMaxDevices = 64;
 cublasHandle_t g_handles[kMaxDevices] = {};
 std::mutex g_handle_mutex;
+int g_gemm_backend = 0;
 
 // One cuBLAS handle per device, created on first use (this allocates; it must
 // therefore happen before any stream capture).
@@ -52,10 +56,10 @@ int check(cublasStatus_t st, const char* what) {
     return AUSSM_ECUDA;
 }
 
-}  // namespace
+bool ok16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Row-major C = A B is issued as column-major C^T = B^T A^T.
-int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, cudaStream_t stream) {
+// ---- library fallback: row-major C = A B issued as column-major C^T = B^T A^T ----
+int lib_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, cudaStream_t stream) {
     cublasHandle_t h;
     if (int rc = get_handle(stream, &h)) return rc;
     const float one = 1.f, zero = 0.f;
@@ -66,8 +70,8 @@ int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w
                  "phase projection GEMM");
 }
 
-int proj_dx(const ProjDims& d, const float* dtheta_w, const float* u, float* dx, bool overwrite,
-            cudaStream_t stream) {
+int lib_dx(const ProjDims& d, const float* dtheta_w, const float* u, float* dx, bool overwrite,
+           cudaStream_t stream) {
     cublasHandle_t h;
     if (int rc = get_handle(stream, &h)) return rc;
     const float one = 1.f, zero = 0.f;
@@ -83,7 +87,7 @@ int proj_dx(const ProjDims& d, const float* dtheta_w, const float* u, float* dx,
     return AUSSM_OK;
 }
 
-int proj_du(const ProjDims& d, const float* dtheta_w, const float* x, float* du, cudaStream_t stream) {
+int lib_du(const ProjDims& d, const float* dtheta_w, const float* x, float* du, cudaStream_t stream) {
     cublasHandle_t h;
     if (int rc = get_handle(stream, &h)) return rc;
     const float one = 1.f;
@@ -92,6 +96,84 @@ int proj_du(const ProjDims& d, const float* dtheta_w, const float* x, float* du,
                                            (long long)M * d.ldw, x, d.D, 0, &one, du + d.t0, (int)d.L,
                                            (long long)d.D * d.L, d.B),
                  "du GEMM");
+}
+
+}  // namespace
+
+void set_gemm_backend(int mode) { g_gemm_backend = mode; }
+
+size_t proj_scratch_floats(int B, int D, int N, long long ldw) {
+    const size_t M = (size_t)D * N;
+    return 2 * M * D + 2 * (size_t)B * D * ldw + 2 * (size_t)B * M * ldw + 64;
+}
+
+void proj_scratch_bind(ProjScratch& s, float* base, int B, int D, int N, long long ldw) {
+    const size_t M = (size_t)D * N;
+    auto up4 = [](size_t v) { return (v + 3) / 4 * 4; };
+    s.x_hi = base;
+    s.x_lo = s.x_hi + up4(M * D);
+    s.u_hi = s.x_lo + up4(M * D);
+    s.u_lo = s.u_hi + up4((size_t)B * D * ldw);
+    s.dth_hi = s.u_lo + up4((size_t)B * D * ldw);
+    s.dth_lo = s.dth_hi + up4((size_t)B * M * ldw);
+    s.use_tensor_cores = 0;
+}
+
+int proj_begin(int B, int D, int N, long long L, long long ldw, const float* x, const float* u, ProjScratch& s,
+               cudaStream_t stream) {
+    (void)B;
+    s.use_tensor_cores = 0;
+    // TMA needs 16-byte aligned rows everywhere: x rows (D floats), u rows (L floats), window rows (ldw floats)
+    const bool aligned = (D % 4 == 0) && (L % 4 == 0) && (ldw % 4 == 0) && ok16(x) && ok16(u) && ok16(s.x_hi);
+    if (g_gemm_backend == 1 || !aligned) return AUSSM_OK;
+    SplitOperand probe = {s.x_hi, s.x_lo, 0, D, 0};
+    GemmShape shape = {D * N, 4, D, 1, 0, 0, ldw, 0};
+    if (!gemm_tf32x3_supported(probe, probe, s.x_hi, shape)) return AUSSM_OK;
+    if (int rc = split_tf32(x, D, 0, s.x_hi, s.x_lo, D, 0, (long long)D * N, D, 1, stream)) return rc;
+    s.use_tensor_cores = 1;
+    return AUSSM_OK;
+}
+
+int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, ProjScratch& s,
+               cudaStream_t stream) {
+    if (!s.use_tensor_cores) return lib_theta(d, x, u, theta_w, stream);
+    const int M = d.D * d.N;
+    // split this window of u: rows r (D of them per batch entry), tl columns
+    if (int rc = split_tf32(u + d.t0, d.L, (long long)d.D * d.L, s.u_hi, s.u_lo, d.ldw, (long long)d.D * d.ldw, d.D,
+                            d.tl, d.B, stream))
+        return rc;
+    // theta_w[b] (M x tl) = x (M x D, K-major) * u_b (D x tl: K rows, N contiguous -> MN-major)
+    const SplitOperand A = {s.x_hi, s.x_lo, 0, d.D, 0};
+    const SplitOperand Bop = {s.u_hi, s.u_lo, 1, d.ldw, (long long)d.D * d.ldw};
+    const GemmShape shape = {M, d.tl, d.D, d.B, 0, 0, d.ldw, (long long)M * d.ldw};
+    return gemm_tf32x3(A, Bop, theta_w, shape, stream);
+}
+
+int proj_adjoints(const ProjDims& d, const float* dtheta_w, const float* x, const float* u, float* dx, float* du,
+                  bool overwrite_dx, ProjScratch& s, cudaStream_t stream) {
+    if (!s.use_tensor_cores) {
+        if (int rc = lib_dx(d, dtheta_w, u, dx, overwrite_dx, stream)) return rc;
+        return lib_du(d, dtheta_w, x, du, stream);
+    }
+    const int M = d.D * d.N;
+    if (int rc = split_tf32(dtheta_w, d.ldw, (long long)M * d.ldw, s.dth_hi, s.dth_lo, d.ldw, (long long)M * d.ldw, M,
+                            d.tl, d.B, stream))
+        return rc;
+    {
+        // dx (M x D) (+)= sum_b dtheta_b (M x tl, K-major) * u_b^T (u_b: D rows x tl, K-major)
+        const SplitOperand A = {s.dth_hi, s.dth_lo, 0, d.ldw, (long long)M * d.ldw};
+        const SplitOperand Bop = {s.u_hi, s.u_lo, 0, d.ldw, (long long)d.D * d.ldw};
+        const GemmShape shape = {M, d.D, d.tl, d.B, 1, overwrite_dx ? 0 : 1, d.D, 0};
+        if (int rc = gemm_tf32x3(A, Bop, dx, shape, stream)) return rc;
+    }
+    {
+        // du_b (D x tl) += x^T (x stored M rows x D: K rows, output-row index contiguous -> MN-major)
+        //                  * dtheta_b (M x tl: K rows, N contiguous -> MN-major)
+        const SplitOperand A = {s.x_hi, s.x_lo, 1, d.D, 0};
+        const SplitOperand Bop = {s.dth_hi, s.dth_lo, 1, d.ldw, (long long)M * d.ldw};
+        const GemmShape shape = {d.D, d.tl, M, d.B, 0, 1, d.L, (long long)d.D * d.L};
+        return gemm_tf32x3(A, Bop, du + d.t0, shape, stream);
+    }
 }
 
 }  // namespace aussm

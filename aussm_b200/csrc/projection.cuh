@@ -5,11 +5,13 @@
 //   du[b][r][t0+t]  += sum_m x[m][r] dtheta_w[b][m][t]
 // (reference: ssm_adaptive_unitary_forward.cu:83-110 builds theta row by row,
 // ssm_adaptive_unitary_backward.cu:419-490 forms the adjoints with atomics.)
-// These are plain dense contractions in float32 (TF32 would put 1e-3 relative
-// error on every phase) and are issued as library GEMMs.
+// These are dense contractions that must keep float32 accuracy (TF32 alone
+// would put 1e-3 relative error on every phase).  Default: the tcgen05 kernel
+// of gemm_tf32x3.cu (three-term TF32 split); fallback: library SGEMM.
 #pragma once
 
 #include <cuda_runtime.h>
+#include <stddef.h>
 
 namespace aussm {
 
@@ -21,11 +23,33 @@ struct ProjDims {
     int tl;
 };
 
+// Scratch for the TF32 hi/lo parts of the operands (caller-owned, inside the operator workspace).
+struct ProjScratch {
+    float* x_hi;      // (D*N, D)
+    float* x_lo;
+    float* u_hi;      // (B, D, ldw)      window of u
+    float* u_lo;
+    float* dth_hi;    // (B, D*N, ldw)    window of dtheta
+    float* dth_lo;
+    int use_tensor_cores;   // decided once per operator call by proj_begin()
+};
+
+// floats needed behind ProjScratch for a window pitch ldw
+size_t proj_scratch_floats(int B, int D, int N, long long ldw);
+void proj_scratch_bind(ProjScratch& s, float* base, int B, int D, int N, long long ldw);
+
+// Chooses the backend for this call and splits x when the tensor-core path is used.
+int proj_begin(int B, int D, int N, long long L, long long ldw, const float* x, const float* u, ProjScratch& s,
+               cudaStream_t stream);
+
 // returns 0 or a negative AUSSM_E* code (message set)
-int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, cudaStream_t stream);
-int proj_dx(const ProjDims& d, const float* dtheta_w, const float* u, float* dx, bool overwrite, cudaStream_t stream);
-int proj_du(const ProjDims& d, const float* dtheta_w, const float* x, float* du, cudaStream_t stream);
+int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, ProjScratch& s,
+               cudaStream_t stream);
+// dx and du from dtheta_w; requires proj_theta() to have run on the same window (it leaves u's split behind)
+int proj_adjoints(const ProjDims& d, const float* dtheta_w, const float* x, const float* u, float* dx, float* du,
+                  bool overwrite_dx, ProjScratch& s, cudaStream_t stream);
 
 void set_error(const char* fmt, ...);
+void set_gemm_backend(int mode);   // 0: tensor cores when the shapes allow, 1: always the library SGEMM
 
 }  // namespace aussm

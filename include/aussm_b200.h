@@ -112,6 +112,23 @@ int aussm_b200_scan_unitary_bwd_static(const float* grad_y, const float* gh1_re,
                                        float* dh0_re, float* dh0_im, int B, int D, int N, int L,
                                        aussm_stream_t stream);
 
+/* ---- float32-accurate tensor-core GEMM -------------------------------------
+ * The contraction behind the phase projection theta = x u and its adjoints
+ * (reference: the per-row loops of ssm_adaptive_unitary_forward.cu:83-110 and
+ * the atomics of ssm_adaptive_unitary_backward.cu:419-490), exposed on its own.
+ * C[M x N] (+)= A * B^T in the sense  C[m][n] = sum_k A(m,k) B(n,k), computed on
+ * the tcgen05 tensor cores as a three-term TF32 split (float32-level accuracy).
+ * Packed operands: x_mn_major == 0: stored (rows, K), K contiguous;
+ * x_mn_major == 1: stored (K, rows), rows contiguous.  `batches` entries follow
+ * each other for an operand with x_batched != 0; a non-batched operand is shared.
+ * reduce_batches != 0: one C = sum over batches; else C holds `batches` M x N
+ * results.  beta: 0 overwrite, 1 accumulate.  K, M (A) / N (B) row lengths must
+ * be multiples of 4 floats. */
+size_t aussm_b200_gemm_tf32x3_workspace_bytes(int M, int N, int K, int batches, int a_batched, int b_batched);
+int aussm_b200_gemm_tf32x3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
+                           int b_batched, float* C, int M, int N, int K, int batches, int reduce_batches, int beta,
+                           void* workspace, size_t workspace_bytes, aussm_stream_t stream);
+
 /* ---- drop-in operators ---------------------------------------------------
  * aussm_b200_unitary_fwd replaces ssm_adaptive_cuda_forward_unitary
  * (ssm_adaptive_unitary_forward.cu:191-277, schema :284) and
