@@ -158,6 +158,7 @@ int aussm_b200_set_option(const char* name, int value) {
     if (!strcmp(name, "fast_trig")) o.fast_trig = value;
     else if (!strcmp(name, "force_plain")) o.force_plain = value;
     else if (!strcmp(name, "variant")) o.variant = value;
+    else if (!strcmp(name, "blocks_per_sm")) o.blocks_per_sm = value;
     else if (!strcmp(name, "gemm_tile")) g_window_override = value;
     else if (!strcmp(name, "gemm_backend")) set_gemm_backend(value);
     else {

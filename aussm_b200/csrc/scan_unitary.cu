@@ -47,7 +47,7 @@ namespace aussm {
 __device__ int g_device_status = 0;
 
 ScanOptions& scan_options() {
-    static ScanOptions o = {0, 0, 0};
+    static ScanOptions o = {0, 0, 0, 0};
     return o;
 }
 
@@ -841,25 +841,39 @@ __global__ void __launch_bounds__(256) reduce_param_grads_kernel(const ReducePar
 // ---------------------------------------------------------------------------
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Dynamic shared memory to request: what the tile shape needs, or more when the caller wants to cap the
+// number of resident blocks per SM (228 KB per SM, 1 KB reserved per block) to fit the grid in whole waves.
+inline size_t padded_smem(size_t needed) {
+    const int want = scan_options().blocks_per_sm;
+    if (want <= 0) return needed;
+    const size_t per_block = (size_t)233472 / (size_t)want;
+    if (per_block <= 1024 + needed) return needed;
+    size_t padded = (per_block - 1024) / 128 * 128;
+    if (padded > 232448) padded = 232448;
+    return padded > needed ? padded : needed;
+}
+
 template <class C, bool ASYNC, bool FAST, bool BIAS>
 cudaError_t launch_fwd_cfg(const ScanFwdParams& p, cudaStream_t stream) {
     auto kern = scan_unitary_fwd_kernel<C, ASYNC, FAST, BIAS>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
+    const size_t smem = padded_smem(C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const long long tasks = ((long long)p.nch + C::CPW - 1) / C::CPW;
     const long long blocks = (tasks + C::WARPS - 1) / C::WARPS;
-    kern<<<(unsigned)blocks, C::WARPS * 32, C::SMEM_BYTES, stream>>>(p);
+    kern<<<(unsigned)blocks, C::WARPS * 32, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
 template <class C, bool ASYNC, bool FAST, bool BIAS>
 cudaError_t launch_bwd_cfg(const ScanBwdParams& p, cudaStream_t stream) {
     auto kern = scan_unitary_bwd_kernel<C, ASYNC, FAST, BIAS>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
+    const size_t smem = padded_smem(C::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const long long tasks = ((long long)p.nch + C::CPW - 1) / C::CPW;
     const long long blocks = (tasks + C::WARPS - 1) / C::WARPS;
-    kern<<<(unsigned)blocks, C::WARPS * 32, C::SMEM_BYTES, stream>>>(p);
+    kern<<<(unsigned)blocks, C::WARPS * 32, smem, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -906,6 +920,8 @@ cudaError_t launch_scan_unitary_fwd(const ScanFwdParams& p_, cudaStream_t stream
         if (o.variant == 1) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 4>>(p, async, fast, stream);
         if (o.variant == 2) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 4>>(p, async, fast, stream);
         if (o.variant == 3) return launch_fwd_sel<FwdCfg<16, 1, 32, 3, 4>>(p, async, fast, stream);
+        if (o.variant == 4) return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 1>>(p, async, fast, stream);
+        if (o.variant == 5) return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 2>>(p, async, fast, stream);
         return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 4>>(p, async, fast, stream);
     }
     if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 32, 2, 4>>(p, async, fast, stream);
@@ -933,7 +949,10 @@ cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p_, cudaStream_t stream
         if (o.variant == 1) return launch_bwd_sel<BwdCfg<8, 2, 32, 32, 2, 2>>(p, async, fast, stream);
         if (o.variant == 2) return launch_bwd_sel<BwdCfg<16, 1, 64, 32, 2, 2>>(p, async, fast, stream);
         if (o.variant == 3) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 3, 2>>(p, async, fast, stream);
-        return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 2>>(p, async, fast, stream);
+        if (o.variant == 4) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 2>>(p, async, fast, stream);
+        if (o.variant == 5) return launch_bwd_sel<BwdCfg<16, 1, 32, 16, 2, 1>>(p, async, fast, stream);
+        // one-warp blocks: a finished warp is replaced at once (measured 9.55 ms against 10.2 ms with two-warp blocks)
+        return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 1>>(p, async, fast, stream);
     }
     if (N <= 32) return launch_bwd_sel<BwdCfg<32, 1, 32, 32, 2, 2>>(p, async, fast, stream);
     if (N <= 64) return launch_bwd_sel<BwdCfg<32, 2, 32, 32, 2, 2>>(p, async, fast, stream);

@@ -91,6 +91,7 @@ struct ScanOptions {
     int fast_trig;   // 1: special-function-unit sin/cos instead of the accurate polynomial
     int force_plain; // 1: never use bulk copies (plain coalesced loads / stores)
     int variant;     // tile-shape variant index, 0 = default
+    int blocks_per_sm; // > 0: pad the dynamic shared memory so that exactly this many blocks fit on an SM
 };
 ScanOptions& scan_options();
 

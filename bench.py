@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--fast-trig", type=int, default=0)
     ap.add_argument("--variant", type=int, default=0)
+    ap.add_argument("--blocks-per-sm", type=int, default=0)
     return ap.parse_args()
 
 
@@ -219,6 +220,7 @@ def run_ours(args):
     lib = _lib.load()
     _lib.set_option("fast_trig", args.fast_trig)
     _lib.set_option("variant", args.variant)
+    _lib.set_option("blocks_per_sm", args.blocks_per_sm)
 
     b, d, n, l = args.batch, args.d_inner, args.d_state, args.seq_len
     elems = b * d * n * l
