@@ -1,0 +1,530 @@
+// Real selective scan ("S6") for sm_100a: forward and backward kernels.
+//
+// Same decomposition as the unitary scan (scan_unitary.cu): one thread owns one
+// state of one channel and walks time sequentially; a warp owns 32/NL channels
+// of ONE batch entry and is independent of every other warp; tiles of 32 steps
+// are staged with coalesced 16-byte asynchronous copies through a two-stage
+// ring.  Here the rows a thread consumes are the B_j and C_j rows of its batch
+// entry (shared by all channels, served from L2), so the path is bound by
+// instruction issue, not by HBM: per (b, i, t) it moves 16 B forward, 28 B
+// backward, for N states of arithmetic.
+//
+// The recurrence contracts (|exp(dlt A)| < 1), so unlike the unitary case it
+// cannot be run backwards: the forward kernel stores the state at the start
+// of every tile (N floats per 32 steps and channel) and the backward kernel
+// recomputes the states of a tile from there before walking it in reverse.
+// dB and dC are sums over the channels of a batch entry: a warp adds its
+// channels with shuffles and then uses float atomics (vector red), as the
+// reference's kernels and mamba-ssm do; all other gradients are deterministic.
+#include "scan_s6.cuh"
+
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace aussm {
+namespace {
+
+constexpr int T = kS6Tile;
+constexpr int TP = T + 4;
+constexpr int STAGES = 2;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int NL_, bool BWD_>
+struct S6Cfg {
+    static constexpr int NL = NL_;
+    static constexpr int CPW = 32 / NL;
+    static constexpr int AUX = BWD_ ? 4 : 3;                      // u, delta, z [, gout]
+    static constexpr int BC_ROWS = 2 * NL;                        // B rows then C rows
+    static constexpr int STAGE_FLOATS = BC_ROWS * TP + CPW * AUX * T;
+    // not staged: forward: dlt/s rows + p tile; backward: dlt/s/w rows + h, Q, Y, P tiles
+    static constexpr int ROWS = BWD_ ? 3 : 2;
+    static constexpr int TILES = BWD_ ? 4 : 1;
+    static constexpr int SCRATCH_FLOATS = CPW * ROWS * T + TILES * 32 * TP;
+    static constexpr int WARP_FLOATS = STAGES * STAGE_FLOATS + SCRATCH_FLOATS;
+    static constexpr size_t SMEM_BYTES = (size_t)WARP_FLOATS * sizeof(float);   // one warp per block
+    static constexpr int NCH_BC = (BC_ROWS * (T / 4) + 31) / 32;
+    static constexpr int NCH_AUX = (CPW * AUX * (T / 4) + 31) / 32;
+    static constexpr int EPL = CPW * T / 32;
+    static constexpr int VW = EPL < 4 ? EPL : 4;
+    static constexpr int ITERS = EPL / VW;
+};
+
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+
+// per-lane sources of the 16-byte pieces of one tile (at step 0)
+template <class C>
+struct S6Map {
+    const float* bc_ptr[C::NCH_BC];
+    const float* aux_ptr[C::NCH_AUX];
+
+    __device__ __forceinline__ void init(int lane, int nvalid, int N, long long L, const float* Bb, const float* Cb,
+                                         long long ch0, const float* const* aux_src) {
+#pragma unroll
+        for (int i = 0; i < C::NCH_BC; ++i) {
+            const int id = i * 32 + lane;
+            const int row = id / (T / 4), col = id % (T / 4);
+            bc_ptr[i] = nullptr;
+            if (row < C::BC_ROWS) {
+                const int j = row % C::NL;
+                const float* base = row < C::NL ? Bb : Cb;
+                bc_ptr[i] = base + (long long)(j < N ? j : 0) * L + col * 4;      // missing states shadow row 0
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < C::NCH_AUX; ++i) {
+            const int id = i * 32 + lane;
+            const int row = id / (T / 4), col = id % (T / 4);
+            aux_ptr[i] = nullptr;
+            if (row < C::CPW * C::AUX) {
+                const int cc = row / C::AUX, a = row % C::AUX;
+                if (aux_src[a] != nullptr) aux_ptr[i] = aux_src[a] + (ch0 + (cc < nvalid ? cc : 0)) * L + col * 4;
+            }
+        }
+    }
+
+    __device__ __forceinline__ void issue(float* stage, long long t0, int tlen, int lane) const {
+        float* aux = stage + C::BC_ROWS * TP;
+#pragma unroll
+        for (int i = 0; i < C::NCH_BC; ++i) {
+            const int id = i * 32 + lane;
+            const int row = id / (T / 4), col = id % (T / 4);
+            if (bc_ptr[i] != nullptr && col * 4 < tlen) cp_async16(stage + row * TP + col * 4, bc_ptr[i] + t0);
+        }
+#pragma unroll
+        for (int i = 0; i < C::NCH_AUX; ++i) {
+            const int id = i * 32 + lane;
+            const int row = id / (T / 4), col = id % (T / 4);
+            if (aux_ptr[i] != nullptr && col * 4 < tlen) cp_async16(aux + row * T + col * 4, aux_ptr[i] + t0);
+        }
+        cp_async_commit();
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Forward
+// ---------------------------------------------------------------------------
+template <int NL>
+__global__ void __launch_bounds__(32) s6_fwd_kernel(const S6FwdParams p) {
+    using C = S6Cfg<NL, false>;
+    constexpr int CPW = C::CPW, AUX = C::AUX, VW = C::VW;
+    extern __shared__ __align__(128) float smem[];
+    const int lane = threadIdx.x;
+    const int tasks_per_batch = (p.Dmod + CPW - 1) / CPW;
+    const int b = blockIdx.x / tasks_per_batch, tw = blockIdx.x % tasks_per_batch;
+    const int i0 = tw * CPW;
+    const int nvalid = min(CPW, p.Dmod - i0);
+    const long long ch0 = (long long)b * p.Dmod + i0;
+    const int c = lane / NL, j = lane % NL;
+    const bool act = c < nvalid && j < p.N;
+    const int N = p.N, L = p.L;
+    const int ntiles = (L + T - 1) / T;
+    const long long ch = ch0 + c;
+
+    float* rows = smem + STAGES * C::STAGE_FLOATS;          // [CPW][2][T]: dlt, s
+    float* pt = rows + CPW * C::ROWS * T;                   // [32][TP]
+
+    const float A2 = act ? p.A[(long long)(i0 + c) * N + j] * kLog2e : 0.f;
+    float h = 0.f;
+    float dval[C::ITERS], bias[C::ITERS];
+#pragma unroll
+    for (int it = 0; it < C::ITERS; ++it) {
+        const int cc = ((lane + 32 * it) * VW) / T;
+        const bool v = cc < nvalid;
+        dval[it] = (v && p.Dskip) ? p.Dskip[i0 + cc] : 0.f;
+        bias[it] = (v && p.delta_bias) ? p.delta_bias[i0 + cc] : 0.f;
+    }
+    const float* aux_src[AUX] = {p.u, p.delta, p.z};
+    S6Map<C> map;
+    map.init(lane, nvalid, N, L, p.Bm + (long long)b * N * L, p.Cm + (long long)b * N * L, ch0, aux_src);
+    for (int s = 0; s < STAGES; ++s) {
+        if (s < ntiles) map.issue(smem + s * C::STAGE_FLOATS, (long long)s * T, min(T, L - s * T), lane);
+        else cp_async_commit();
+    }
+
+    for (int tile = 0; tile < ntiles; ++tile) {
+        float* st = smem + (tile % STAGES) * C::STAGE_FLOATS;
+        float* aux = st + C::BC_ROWS * TP;
+        const long long t0 = (long long)tile * T;
+        const int tlen = min(T, L - (int)t0);
+        const int nq = tlen >> 2;
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+        if (act && p.ckpt) p.ckpt[(ch * N + j) * ntiles + tile] = h;
+
+        // pre-pass: dlt = softplus(delta + bias), s = dlt * u
+#pragma unroll
+        for (int it = 0; it < C::ITERS; ++it) {
+            const int e0 = (lane + 32 * it) * VW;
+            const int cc = e0 / T, t = e0 % T;
+            if (t < tlen) {
+                Vec<VW> u, d, s;
+                u.ld(aux + (cc * AUX + 0) * T + t);
+                d.ld(aux + (cc * AUX + 1) * T + t);
+#pragma unroll
+                for (int e = 0; e < VW; ++e) {
+                    float x = d.v[e] + bias[it];
+                    if (p.delta_softplus) x = softplusf_(x);
+                    d.v[e] = x;
+                    s.v[e] = x * u.v[e];
+                }
+                d.st(rows + (cc * 2 + 0) * T + t);
+                s.st(rows + (cc * 2 + 1) * T + t);
+            }
+        }
+        __syncwarp();
+
+        for (int q = 0; q < nq; ++q) {
+            const float4 d4 = ld_shared_f4(rows + (c * 2 + 0) * T + 4 * q);
+            const float4 s4 = ld_shared_f4(rows + (c * 2 + 1) * T + 4 * q);
+            const float4 b4 = ld_shared_f4(st + j * TP + 4 * q);
+            const float4 c4 = ld_shared_f4(st + (NL + j) * TP + 4 * q);
+            const float dv[4] = {d4.x, d4.y, d4.z, d4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+            const float bv[4] = {b4.x, b4.y, b4.z, b4.w}, cv[4] = {c4.x, c4.y, c4.z, c4.w};
+            float pv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float a = exp2f(dv[e] * A2);
+                h = fmaf(a, h, sv[e] * bv[e]);
+                pv[e] = act ? cv[e] * h : 0.f;
+            }
+            st_shared_f4(pt + lane * TP + 4 * q, make_float4(pv[0], pv[1], pv[2], pv[3]));
+        }
+        __syncwarp();
+
+        // post-pass: out = (sum_j p + D u) * silu(z)
+#pragma unroll
+        for (int it = 0; it < C::ITERS; ++it) {
+            const int e0 = (lane + 32 * it) * VW;
+            const int cc = e0 / T, t = e0 % T;
+            if (t < tlen && cc < nvalid) {
+                Vec<VW> acc, u, z;
+#pragma unroll
+                for (int e = 0; e < VW; ++e) acc.v[e] = 0.f;
+#pragma unroll
+                for (int r = 0; r < NL; ++r) {
+                    Vec<VW> v;
+                    v.ld(pt + (cc * NL + r) * TP + t);
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) acc.v[e] += v.v[e];
+                }
+                u.ld(aux + (cc * AUX + 0) * T + t);
+#pragma unroll
+                for (int e = 0; e < VW; ++e) acc.v[e] = fmaf(dval[it], u.v[e], acc.v[e]);
+                if (p.z) {
+                    z.ld(aux + (cc * AUX + 2) * T + t);
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) acc.v[e] *= siluf_(z.v[e]);
+                }
+                acc.st(p.out + (ch0 + cc) * L + t0 + t);
+            }
+        }
+        __syncwarp();
+        const int nt = tile + STAGES;
+        if (nt < ntiles) map.issue(st, (long long)nt * T, min(T, L - nt * T), lane);
+        else cp_async_commit();
+    }
+    cp_async_wait<0>();
+    if (act && p.last_state) p.last_state[ch * N + j] = h;
+}
+
+// ---------------------------------------------------------------------------
+// Backward
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+
+template <int NL>
+__global__ void __launch_bounds__(32) s6_bwd_kernel(const S6BwdParams p) {
+    using C = S6Cfg<NL, true>;
+    constexpr int CPW = C::CPW, AUX = C::AUX, VW = C::VW;
+    extern __shared__ __align__(128) float smem[];
+    const int lane = threadIdx.x;
+    const int tasks_per_batch = (p.Dmod + CPW - 1) / CPW;
+    const int b = blockIdx.x / tasks_per_batch, tw = blockIdx.x % tasks_per_batch;
+    const int i0 = tw * CPW;
+    const int nvalid = min(CPW, p.Dmod - i0);
+    const long long ch0 = (long long)b * p.Dmod + i0;
+    const int c = lane / NL, j = lane % NL;
+    const bool act = c < nvalid && j < p.N;
+    const int N = p.N, L = p.L;
+    const int ntiles = (L + T - 1) / T;
+    const long long ch = ch0 + c;
+
+    float* rows = smem + STAGES * C::STAGE_FLOATS;          // [CPW][3][T]: dlt, s, w
+    float* hp = rows + CPW * C::ROWS * T;                   // [32][TP] state before each step
+    float* qt = hp + 32 * TP;                               // [32][TP] eta h_prev a A   (-> d dlt)
+    float* yt = qt + 32 * TP;                               // [32][TP] eta B            (-> d dlt, d u)
+    float* pt = yt + 32 * TP;                               // [32][TP] C h              (-> d z)
+
+    const float A1 = act ? p.A[(long long)(i0 + c) * N + j] : 0.f;
+    const float A2 = A1 * kLog2e;
+    float eps = 0.f;        // a_{t+1} eta_{t+1}
+    float dA_acc = 0.f;
+    float dval[C::ITERS], bias[C::ITERS], dD_acc[C::ITERS], db_acc[C::ITERS];
+#pragma unroll
+    for (int it = 0; it < C::ITERS; ++it) {
+        const int cc = ((lane + 32 * it) * VW) / T;
+        const bool v = cc < nvalid;
+        dval[it] = (v && p.Dskip) ? p.Dskip[i0 + cc] : 0.f;
+        bias[it] = (v && p.delta_bias) ? p.delta_bias[i0 + cc] : 0.f;
+        dD_acc[it] = db_acc[it] = 0.f;
+    }
+    const float* aux_src[AUX] = {p.u, p.delta, p.z, p.gout};
+    S6Map<C> map;
+    map.init(lane, nvalid, N, L, p.Bm + (long long)b * N * L, p.Cm + (long long)b * N * L, ch0, aux_src);
+    for (int r = 0; r < STAGES; ++r) {
+        const int tile = ntiles - 1 - r;
+        if (tile >= 0) map.issue(smem + r * C::STAGE_FLOATS, (long long)tile * T, min(T, L - tile * T), lane);
+        else cp_async_commit();
+    }
+    const float* ck = p.ckpt + (act ? (ch * N + j) * ntiles : 0);
+    float h_next_start = act ? ck[ntiles - 1] : 0.f;
+
+    for (int r = 0; r < ntiles; ++r) {
+        const int tile = ntiles - 1 - r;
+        float* st = smem + (r % STAGES) * C::STAGE_FLOATS;
+        float* aux = st + C::BC_ROWS * TP;
+        const long long t0 = (long long)tile * T;
+        const int tlen = min(T, L - (int)t0);
+        const int nq = tlen >> 2;
+        float h = h_next_start;
+        if (tile > 0 && act) h_next_start = ck[tile - 1];      // prefetch the next tile's start state
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+
+        // pre-pass: dlt, s = dlt u, w = gout silu(z)
+#pragma unroll
+        for (int it = 0; it < C::ITERS; ++it) {
+            const int e0 = (lane + 32 * it) * VW;
+            const int cc = e0 / T, t = e0 % T;
+            if (t < tlen) {
+                Vec<VW> u, d, s, w;
+                u.ld(aux + (cc * AUX + 0) * T + t);
+                d.ld(aux + (cc * AUX + 1) * T + t);
+                w.ld(aux + (cc * AUX + 3) * T + t);
+                if (p.z) {
+                    Vec<VW> z;
+                    z.ld(aux + (cc * AUX + 2) * T + t);
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) w.v[e] *= siluf_(z.v[e]);
+                }
+#pragma unroll
+                for (int e = 0; e < VW; ++e) {
+                    float x = d.v[e] + bias[it];
+                    if (p.delta_softplus) x = softplusf_(x);
+                    d.v[e] = x;
+                    s.v[e] = x * u.v[e];
+                }
+                d.st(rows + (cc * 3 + 0) * T + t);
+                s.st(rows + (cc * 3 + 1) * T + t);
+                w.st(rows + (cc * 3 + 2) * T + t);
+            }
+        }
+        __syncwarp();
+
+        // recompute the states of the tile; keep the state BEFORE each step
+        for (int q = 0; q < nq; ++q) {
+            const float4 d4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
+            const float4 s4 = ld_shared_f4(rows + (c * 3 + 1) * T + 4 * q);
+            const float4 b4 = ld_shared_f4(st + j * TP + 4 * q);
+            const float dv[4] = {d4.x, d4.y, d4.z, d4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+            const float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+            float hv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                hv[e] = h;
+                h = fmaf(exp2f(dv[e] * A2), h, sv[e] * bv[e]);
+            }
+            st_shared_f4(hp + lane * TP + 4 * q, make_float4(hv[0], hv[1], hv[2], hv[3]));
+        }
+
+        // reverse pass
+        for (int q = nq - 1; q >= 0; --q) {
+            const float4 d4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
+            const float4 s4 = ld_shared_f4(rows + (c * 3 + 1) * T + 4 * q);
+            const float4 w4 = ld_shared_f4(rows + (c * 3 + 2) * T + 4 * q);
+            const float4 b4 = ld_shared_f4(st + j * TP + 4 * q);
+            const float4 c4 = ld_shared_f4(st + (NL + j) * TP + 4 * q);
+            const float4 h4 = ld_shared_f4(hp + lane * TP + 4 * q);
+            const float dv[4] = {d4.x, d4.y, d4.z, d4.w}, sv[4] = {s4.x, s4.y, s4.z, s4.w};
+            const float wv[4] = {w4.x, w4.y, w4.z, w4.w}, bv[4] = {b4.x, b4.y, b4.z, b4.w};
+            const float cv[4] = {c4.x, c4.y, c4.z, c4.w}, hv[4] = {h4.x, h4.y, h4.z, h4.w};
+            float Q[4], Y[4], P[4], gB[4], gC[4];
+#pragma unroll
+            for (int e = 3; e >= 0; --e) {
+                const float a = exp2f(dv[e] * A2);
+                const float ht = fmaf(a, hv[e], sv[e] * bv[e]);       // h_t
+                const float g = fmaf(cv[e], wv[e], eps);               // eta_t
+                const float qa = g * hv[e] * a;                        // eta_t h_{t-1} a_t
+                dA_acc = fmaf(qa, dv[e], dA_acc);
+                Q[e] = act ? qa * A1 : 0.f;
+                Y[e] = act ? g * bv[e] : 0.f;
+                P[e] = act ? cv[e] * ht : 0.f;
+                gB[e] = act ? g * sv[e] : 0.f;
+                gC[e] = act ? wv[e] * ht : 0.f;
+                eps = a * g;
+            }
+            st_shared_f4(qt + lane * TP + 4 * q, make_float4(Q[0], Q[1], Q[2], Q[3]));
+            st_shared_f4(yt + lane * TP + 4 * q, make_float4(Y[0], Y[1], Y[2], Y[3]));
+            st_shared_f4(pt + lane * TP + 4 * q, make_float4(P[0], P[1], P[2], P[3]));
+            // dB, dC: add the warp's channels, then one vector atomic per state and quad
+#pragma unroll
+            for (int off = NL; off < 32; off <<= 1) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    gB[e] += __shfl_xor_sync(0xffffffffu, gB[e], off);
+                    gC[e] += __shfl_xor_sync(0xffffffffu, gC[e], off);
+                }
+            }
+            if (c == 0 && j < N) {
+                const long long o = ((long long)b * N + j) * L + t0 + 4 * q;
+                red_add_v4(p.dB + o, gB[0], gB[1], gB[2], gB[3]);
+                red_add_v4(p.dC + o, gC[0], gC[1], gC[2], gC[3]);
+            }
+        }
+        __syncwarp();
+
+        // post-pass: du, ddelta, dz
+#pragma unroll
+        for (int it = 0; it < C::ITERS; ++it) {
+            const int e0 = (lane + 32 * it) * VW;
+            const int cc = e0 / T, t = e0 % T;
+            if (t < tlen && cc < nvalid) {
+                Vec<VW> SQ, SY, SP, u, draw, dl, w, g, z, du, dd, dz;
+#pragma unroll
+                for (int e = 0; e < VW; ++e) SQ.v[e] = SY.v[e] = SP.v[e] = 0.f;
+#pragma unroll
+                for (int rr = 0; rr < NL; ++rr) {
+                    Vec<VW> a, bb, cc2;
+                    a.ld(qt + (cc * NL + rr) * TP + t);
+                    bb.ld(yt + (cc * NL + rr) * TP + t);
+                    cc2.ld(pt + (cc * NL + rr) * TP + t);
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) { SQ.v[e] += a.v[e]; SY.v[e] += bb.v[e]; SP.v[e] += cc2.v[e]; }
+                }
+                u.ld(aux + (cc * AUX + 0) * T + t);
+                draw.ld(aux + (cc * AUX + 1) * T + t);
+                g.ld(aux + (cc * AUX + 3) * T + t);
+                dl.ld(rows + (cc * 3 + 0) * T + t);
+                w.ld(rows + (cc * 3 + 2) * T + t);
+                if (p.z) z.ld(aux + (cc * AUX + 2) * T + t);
+#pragma unroll
+                for (int e = 0; e < VW; ++e) {
+                    float ddl = fmaf(u.v[e], SY.v[e], SQ.v[e]);                       // d dlt
+                    if (p.delta_softplus) ddl *= sigmoidf_(draw.v[e] + bias[it]);     // softplus'
+                    dd.v[e] = ddl;
+                    du.v[e] = fmaf(dl.v[e], SY.v[e], w.v[e] * dval[it]);
+                    db_acc[it] += ddl;
+                    dD_acc[it] = fmaf(w.v[e], u.v[e], dD_acc[it]);
+                    if (p.z) {
+                        float gz;
+                        silu_and_grad(z.v[e], gz);
+                        dz.v[e] = g.v[e] * fmaf(dval[it], u.v[e], SP.v[e]) * gz;
+                    }
+                }
+                const long long off = (ch0 + cc) * L + t0 + t;
+                du.st(p.du + off);
+                dd.st(p.ddelta + off);
+                if (p.z) dz.st(p.dz + off);
+            }
+        }
+        __syncwarp();
+        const int nr = r + STAGES;
+        if (nr < ntiles) {
+            const int nt = ntiles - 1 - nr;
+            map.issue(st, (long long)nt * T, min(T, L - nt * T), lane);
+        } else {
+            cp_async_commit();
+        }
+    }
+    cp_async_wait<0>();
+
+    if (act) p.part_A[ch * N + j] = dA_acc;
+    // per-channel sums of dD and d(delta_bias) through a scratch tile
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < C::ITERS; ++it) {
+        qt[lane + 32 * it] = dD_acc[it];
+        yt[lane + 32 * it] = db_acc[it];
+    }
+    __syncwarp();
+    if (lane < nvalid) {
+        float aD = 0.f, ab = 0.f;
+        for (int idx = 0; idx < 32 * C::ITERS; ++idx)
+            if ((idx * VW) / T == lane) { aD += qt[idx]; ab += yt[idx]; }
+        p.part_D[ch0 + lane] = aD;
+        p.part_bias[ch0 + lane] = ab;
+    }
+}
+
+__global__ void __launch_bounds__(256) s6_reduce_kernel(const S6ReduceParams p) {
+    const long long o = (long long)blockIdx.x * 256 + threadIdx.x;
+    const long long DN = (long long)p.D * p.N;
+    if (o < DN) {
+        float acc = 0.f;
+        for (int b = 0; b < p.batch; ++b) acc += p.part_A[(long long)b * DN + o];
+        p.dA[o] = acc;
+    } else if (o < DN + p.D) {
+        const long long i = o - DN;
+        float aD = 0.f, ab = 0.f;
+        for (int b = 0; b < p.batch; ++b) {
+            aD += p.part_D[(long long)b * p.D + i];
+            ab += p.part_bias[(long long)b * p.D + i];
+        }
+        if (p.dD) p.dD[i] = aD;
+        if (p.dbias) p.dbias[i] = ab;
+    }
+}
+
+template <int NL>
+cudaError_t launch_fwd_nl(const S6FwdParams& p, cudaStream_t stream) {
+    using C = S6Cfg<NL, false>;
+    auto kern = s6_fwd_kernel<NL>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    const long long blocks = (long long)(p.nch / p.Dmod) * ((p.Dmod + C::CPW - 1) / C::CPW);
+    kern<<<(unsigned)blocks, 32, C::SMEM_BYTES, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int NL>
+cudaError_t launch_bwd_nl(const S6BwdParams& p, cudaStream_t stream) {
+    using C = S6Cfg<NL, true>;
+    auto kern = s6_bwd_kernel<NL>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    const long long blocks = (long long)(p.nch / p.Dmod) * ((p.Dmod + C::CPW - 1) / C::CPW);
+    kern<<<(unsigned)blocks, 32, C::SMEM_BYTES, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_s6_fwd(const S6FwdParams& p, cudaStream_t stream) {
+    if (p.nch <= 0 || p.L <= 0) return cudaSuccess;
+    if (p.N <= 4) return launch_fwd_nl<4>(p, stream);
+    if (p.N <= 8) return launch_fwd_nl<8>(p, stream);
+    if (p.N <= 16) return launch_fwd_nl<16>(p, stream);
+    if (p.N <= 32) return launch_fwd_nl<32>(p, stream);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_s6_bwd(const S6BwdParams& p, cudaStream_t stream) {
+    if (p.nch <= 0 || p.L <= 0) return cudaSuccess;
+    if (p.N <= 4) return launch_bwd_nl<4>(p, stream);
+    if (p.N <= 8) return launch_bwd_nl<8>(p, stream);
+    if (p.N <= 16) return launch_bwd_nl<16>(p, stream);
+    if (p.N <= 32) return launch_bwd_nl<32>(p, stream);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_s6_reduce(const S6ReduceParams& p, cudaStream_t stream) {
+    const long long total = (long long)p.D * p.N + p.D;
+    s6_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace aussm

@@ -159,6 +159,33 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
                            float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
                            aussm_stream_t stream);
 
+/* ---- real selective scan of the Mamba block ("S6") -------------------------
+ * The reference's MambaBlock calls mamba_ssm.selective_scan_fn, a third-party
+ * CUDA extension that is not part of the reference tree
+ * (ai-modules/wavesAI/model/aussm.py:30, :791-802); these entry points provide
+ * that operator with the call site's semantics:
+ *   dlt = delta + delta_bias[i], through softplus when delta_softplus != 0
+ *   h_t = exp(dlt_t A[i][j]) h_{t-1} + dlt_t Bm[b][j][t] u[b][i][t]
+ *   out = (sum_j Cm[b][j][t] h_t + Dskip[i] u) * silu(z)        (Dskip, z, delta_bias may be NULL)
+ * u, delta, z, out: (B, D, L); A: (D, N); Bm, Cm: (B, N, L).  L must be a
+ * multiple of 4 and N <= 32.  `ckpt` (aussm_b200_selective_scan_ckpt_floats
+ * floats) receives the state at every 32nd step and is what the backward pass
+ * restarts from (NULL when no backward pass will follow).  dB and dC are summed
+ * over the channels with float atomics (as in mamba-ssm), so they are
+ * reproducible only up to rounding; everything else is deterministic. */
+size_t aussm_b200_selective_scan_ckpt_floats(int B, int D, int N, int L);
+size_t aussm_b200_selective_scan_bwd_workspace_bytes(int B, int D, int N, int L);
+int aussm_b200_selective_scan_fwd(const float* u, const float* delta, const float* A, const float* Bm,
+                                  const float* Cm, const float* Dskip, const float* z, const float* delta_bias,
+                                  int delta_softplus, float* out, float* ckpt, float* last_state, int B, int D, int N,
+                                  int L, aussm_stream_t stream);
+int aussm_b200_selective_scan_bwd(const float* gout, const float* u, const float* delta, const float* A,
+                                  const float* Bm, const float* Cm, const float* Dskip, const float* z,
+                                  const float* delta_bias, int delta_softplus, const float* ckpt, float* du,
+                                  float* ddelta, float* dA, float* dB, float* dC, float* dD, float* dz,
+                                  float* ddelta_bias, int B, int D, int N, int L, void* workspace,
+                                  size_t workspace_bytes, aussm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
