@@ -28,6 +28,10 @@ SIGNATURES = {
     "aussm_b200_gemm_tf32x3_workspace_bytes": (_Z, [_I] * 6),
     "aussm_b200_gemm_tf32x3": (_I, [_P, _I, _I, _P, _I, _I, _P] + [_I] * 6 + [_P, _Z, _P]),
     "aussm_b200_unitary_workspace_bytes": (_Z, [_I] * 4),
+    "aussm_b200_scan_complex_ckpt_floats": (_Z, [_I] * 4),
+    "aussm_b200_scan_complex_bwd_workspace_bytes": (_Z, [_I] * 4),
+    "aussm_b200_scan_complex_fwd": (_I, [_P] * 12 + [_I] * 4 + [_P]),
+    "aussm_b200_scan_complex_bwd": (_I, [_P] * 22 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_selective_scan_ckpt_floats": (_Z, [_I] * 4),
     "aussm_b200_selective_scan_bwd_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_selective_scan_fwd": (_I, [_P] * 8 + [_I] + [_P] * 3 + [_I] * 4 + [_P]),

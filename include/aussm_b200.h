@@ -186,6 +186,31 @@ int aussm_b200_selective_scan_bwd(const float* gout, const float* u, const float
                                   float* ddelta_bias, int B, int D, int N, int L, void* workspace,
                                   size_t workspace_bytes, aussm_stream_t stream);
 
+/* ---- general complex / positive-real scan ----------------------------------
+ * The recurrence of the reference's ssm_adaptive_complex and
+ * ssm_adaptive_preal kernels (csrc/cuda/ssm_adaptive_complex.cu:181-744,
+ * ssm_adaptive_real.cu:115-560; compiled but never registered there) on a
+ * given eigenvalue:  lambda_t = exp(rho_t + i theta_t),
+ *   h_t = lambda_t h_{t-1} + Bc[b][j][t] dt_t silu(u_t),
+ *   y_t = silu(z_t) (Dskip_i silu(u_t) + sum_j Re(Cc[b][j][t] h_t)).
+ * rho, theta, drho, dtheta: (B, D, N, L) (either input may be NULL = 0);
+ * B_re, B_im, C_re, C_im and their gradients: (B, N, L) (imaginary parts may
+ * be NULL = 0: positive-real variant).  L multiple of 4, N <= 32.  `ckpt`
+ * (aussm_b200_scan_complex_ckpt_floats floats) receives the state at every
+ * 32nd step, from which the backward pass restarts.  dB / dC use float atomics. */
+size_t aussm_b200_scan_complex_ckpt_floats(int B, int D, int N, int L);
+size_t aussm_b200_scan_complex_bwd_workspace_bytes(int B, int D, int N, int L);
+int aussm_b200_scan_complex_fwd(const float* rho, const float* theta, const float* u, const float* dt,
+                                const float* z, const float* B_re, const float* B_im, const float* C_re,
+                                const float* C_im, const float* Dskip, float* y, float* ckpt, int B, int D, int N,
+                                int L, aussm_stream_t stream);
+int aussm_b200_scan_complex_bwd(const float* gy, const float* rho, const float* theta, const float* u,
+                                const float* dt, const float* z, const float* B_re, const float* B_im,
+                                const float* C_re, const float* C_im, const float* Dskip, const float* ckpt,
+                                float* drho, float* dtheta, float* du, float* ddt, float* dz, float* dB_re,
+                                float* dB_im, float* dC_re, float* dC_im, float* dD, int B, int D, int N, int L,
+                                void* workspace, size_t workspace_bytes, aussm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
