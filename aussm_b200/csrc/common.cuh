@@ -100,7 +100,20 @@ __device__ __forceinline__ void bulk_wait_all() {
 // Activations (the reference's sigmoid / silu / d_silu,
 // csrc/cuda/ssm_adaptive_commons.h:92-112, in float32).
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// Special-function-unit exponential and reciprocal in their flush-to-zero forms (one instruction each, no
+// range fix-up, about 2 ulp): 1 + 2^(-x log2 e) is at least 1, so nothing near the subnormal range is inverted,
+// and an exponential that underflows to zero gives sigmoid = 1 exactly as it should.
+__device__ __forceinline__ float ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_ftz(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * x)); }
 
 __device__ __forceinline__ float siluf_(float x) { return x * sigmoidf_(x); }
 
@@ -213,6 +226,10 @@ __device__ __forceinline__ void sincos4(const float (&th)[4], float (&sn)[4], fl
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(dst_smem)), "l"(src_gmem) : "memory");
 }
+// same copy with the destination given as a 32-bit shared-window address (lets base + immediate fold)
+__device__ __forceinline__ void cp_async16_s(uint32_t dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src_gmem) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -225,16 +242,26 @@ template <> struct Vec<1> {
     float v[1];
     __device__ __forceinline__ void ld(const float* p) { v[0] = *p; }
     __device__ __forceinline__ void st(float* p) const { *p = v[0]; }
+    __device__ __forceinline__ void add(const Vec<1>& o) { v[0] += o.v[0]; }
 };
 template <> struct Vec<2> {
     float v[2];
     __device__ __forceinline__ void ld(const float* p) { float2 t = *reinterpret_cast<const float2*>(p); v[0] = t.x; v[1] = t.y; }
     __device__ __forceinline__ void st(float* p) const { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+    __device__ __forceinline__ void add(const Vec<2>& o) {       // one packed add
+        const float2 r = __fadd2_rn(make_float2(v[0], v[1]), make_float2(o.v[0], o.v[1]));
+        v[0] = r.x; v[1] = r.y;
+    }
 };
 template <> struct Vec<4> {
     float v[4];
     __device__ __forceinline__ void ld(const float* p) { float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
     __device__ __forceinline__ void st(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+    __device__ __forceinline__ void add(const Vec<4>& o) {       // two packed adds
+        const float2 a = __fadd2_rn(make_float2(v[0], v[1]), make_float2(o.v[0], o.v[1]));
+        const float2 b = __fadd2_rn(make_float2(v[2], v[3]), make_float2(o.v[2], o.v[3]));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
 };
 
 __device__ __forceinline__ float4 ld_shared_f4(const float* p) { return *reinterpret_cast<const float4*>(p); }

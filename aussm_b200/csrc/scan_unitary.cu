@@ -42,6 +42,10 @@
 #include "common.cuh"
 #include "scan_unitary.cuh"
 
+#ifndef AUSSM_PROBE
+#define AUSSM_PROBE 0
+#endif
+
 namespace aussm {
 
 __device__ int g_device_status = 0;
@@ -83,8 +87,8 @@ struct Cfg {
     static constexpr int TSP = TS + 4;
     static constexpr int NROWS = 32 * SPT;
     static constexpr int STAGE_FLOATS = NROWS * TP + CPW * AUX * T;
-    // backward only, not staged: two column-sum tiles and the s / w rows of a sub-block
-    static constexpr int SCRATCH_FLOATS = BWD_ ? 2 * 32 * TSP + CPW * 2 * TS : 0;
+    // backward only, not staged: two column-sum tiles and the s / w / silu'(u) rows of a sub-block
+    static constexpr int SCRATCH_FLOATS = BWD_ ? 2 * 32 * TSP + CPW * 3 * TS : 0;
     static constexpr int WARP_FLOATS = STAGES * STAGE_FLOATS + SCRATCH_FLOATS;
     static constexpr size_t SMEM_BYTES = (size_t)WARPS * WARP_FLOATS * sizeof(float);
     // asynchronous-copy instructions per lane and tile
@@ -198,23 +202,34 @@ struct TileMap {
         }
     }
 
-    // queue the asynchronous copies of one tile and close the group
-    __device__ __forceinline__ void issue(float* stage, const float* theta_warp, long long t0, int tlen,
-                                          int lane) const {
-        float* aux = stage + C::NROWS * C::TP;
+    // queue the asynchronous copies of one tile and close the group (FULL: a whole tile, no per-piece bound check).
+    // Piece i of a lane lands at a compile-time distance from the lane's first piece, so every destination is
+    // one register plus an immediate.
+    template <bool FULL>
+    __device__ __forceinline__ void issue_t(float* stage, const float* theta_t0, long long t0, int tlen,
+                                            int lane) const {
+        constexpr int CPR = C::CHUNKS_PER_ROW, RPI = 32 / CPR;       // rows covered by one warp-wide instruction
+        static_assert(32 % CPR == 0, "pieces per row must divide the warp");
+        const int col = lane % CPR;
+        const uint32_t dst0 = smem_addr(stage) + (uint32_t)(((lane / CPR) * C::TP + col * 4) * sizeof(float));
 #pragma unroll
         for (int i = 0; i < C::NCH_THETA; ++i) {
-            const int id = i * 32 + lane;
-            const int slot = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
-            if (col * 4 < tlen) cp_async16(stage + slot * C::TP + col * 4, theta_warp + theta_off[i] + t0);
+            if (FULL || col * 4 < tlen)
+                cp_async16_s(dst0 + (uint32_t)(i * RPI * C::TP * sizeof(float)), theta_t0 + theta_off[i]);
         }
+        const uint32_t aux0 = smem_addr(stage) +
+                              (uint32_t)((C::NROWS * C::TP + (lane / CPR) * C::T + col * 4) * sizeof(float));
 #pragma unroll
         for (int i = 0; i < C::NCH_AUX; ++i) {
-            const int id = i * 32 + lane;
-            const int row = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
-            if (aux_ptr[i] != nullptr && col * 4 < tlen) cp_async16(aux + row * C::T + col * 4, aux_ptr[i] + t0);
+            if (aux_ptr[i] != nullptr && (FULL || col * 4 < tlen))
+                cp_async16_s(aux0 + (uint32_t)(i * RPI * C::T * sizeof(float)), aux_ptr[i] + t0);
         }
         cp_async_commit();
+    }
+    __device__ __forceinline__ void issue(float* stage, const float* theta_warp, long long t0, int tlen,
+                                          int lane) const {
+        if (tlen == C::T) issue_t<true>(stage, theta_warp + t0, t0, tlen, lane);
+        else issue_t<false>(stage, theta_warp + t0, t0, tlen, lane);
     }
 };
 
@@ -302,9 +317,9 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
             plain_load_tile<C>(th, theta_warp, p.ld_theta, aux_src, p.ld_row, ch0, nvalid, N, t0, tlen, lane);
         }
 
-        // pre-pass: s = dt * silu(u) over the dt row
+        // pre-pass: v = silu(u) over the u row, s = dt * v over the dt row
 #pragma unroll
-        for (int it = 0; it < C::ITERS; ++it) {
+        for (int it = 0; it < ((AUSSM_PROBE & 4) ? 0 : C::ITERS); ++it) {
             const int e0 = (lane + 32 * it) * VW;
             const int cc = e0 / T, t = e0 % T;
             if (t < tlen) {
@@ -312,7 +327,11 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
                 u.ld(aux + (cc * AUX + 0) * T + t);
                 d.ld(aux + (cc * AUX + 1) * T + t);
 #pragma unroll
-                for (int e = 0; e < VW; ++e) d.v[e] *= siluf_(u.v[e]);
+                for (int e = 0; e < VW; ++e) {
+                    u.v[e] = siluf_(u.v[e]);
+                    d.v[e] *= u.v[e];
+                }
+                u.st(aux + (cc * AUX + 0) * T + t);      // the u row now holds silu(u) for the post-pass
                 d.st(aux + (cc * AUX + 1) * T + t);
             }
         }
@@ -320,7 +339,7 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
 
         // scan: SPT states per thread, four steps per shared-memory access
         const float* srow = aux + (c * AUX + 1) * T;
-        for (int q = 0; q < nq; ++q) {
+        auto quad = [&](const int q) {
             const float4 s4 = ld_shared_f4(srow + 4 * q);
             const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
             float pacc[4];
@@ -350,36 +369,39 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
                     }
                     hr[k] = nr;
                     hi[k] = ni;
-                    const float pv = fmaf(sc[k].mr, nr, -sc[k].mi * ni);
-                    pacc[e] = (k == 0) ? pv : pacc[e] + pv;
+                    pacc[e] = (k == 0) ? fmaf(sc[k].mr, nr, -sc[k].mi * ni)
+                                       : fmaf(sc[k].mr, nr, fmaf(-sc[k].mi, ni, pacc[e]));
                 }
             }
             st_shared_f4(th + lane * TP + 4 * q, make_float4(pacc[0], pacc[1], pacc[2], pacc[3]));
+        };
+        if (ASYNC && tlen == T) {
+#pragma unroll
+            for (int q = 0; q < T / 4; ++q) quad(q);
+        } else {
+            for (int q = 0; q < nq; ++q) quad(q);
         }
         __syncwarp();
 
         // post-pass: one lane = one channel and VW steps
-        if (p.y) {
+        if (p.y && !(AUSSM_PROBE & 2)) {
 #pragma unroll
             for (int it = 0; it < C::ITERS; ++it) {
                 const int e0 = (lane + 32 * it) * VW;
                 const int cc = e0 / T, t = e0 % T;
                 if (t < tlen && cc < nvalid) {
                     Vec<VW> acc, u, z;
+                    acc.ld(th + cc * NL * TP + t);
 #pragma unroll
-                    for (int e = 0; e < VW; ++e) acc.v[e] = 0.f;
-#pragma unroll
-                    for (int r = 0; r < NL; ++r) {
+                    for (int r = 1; r < NL; ++r) {
                         Vec<VW> v;
                         v.ld(th + (cc * NL + r) * TP + t);
-#pragma unroll
-                        for (int e = 0; e < VW; ++e) acc.v[e] += v.v[e];
+                        acc.add(v);
                     }
-                    u.ld(aux + (cc * AUX + 0) * T + t);
+                    u.ld(aux + (cc * AUX + 0) * T + t);      // silu(u), left by the pre-pass
                     z.ld(aux + (cc * AUX + 2) * T + t);
 #pragma unroll
-                    for (int e = 0; e < VW; ++e)
-                        acc.v[e] = siluf_(z.v[e]) * fmaf(dval[it], siluf_(u.v[e]), acc.v[e]);
+                    for (int e = 0; e < VW; ++e) acc.v[e] = siluf_(z.v[e]) * fmaf(dval[it], u.v[e], acc.v[e]);
                     float* dst = p.y + (ch0 + cc) * p.ld_row + t0 + t;
                     if (ASYNC) {
                         acc.st(dst);      // global pointers take the same vector stores
@@ -393,8 +415,12 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
         __syncwarp();
         if (ASYNC) {
             const int nt = tile + STAGES;
+#if (AUSSM_PROBE & 1)
+            cp_async_commit();
+#else
             if (nt < ntiles) map.issue(th, theta_warp, (long long)nt * T, min(T, L - nt * T), lane);
             else cp_async_commit();
+#endif
         }
     }
     if (ASYNC) cp_async_wait<0>();
@@ -465,7 +491,7 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
     float* scratch = wsm + STAGES * C::STAGE_FLOATS;
     float* pt = scratch;                    // [32][TSP] projections, summed over a thread's states
     float* et = pt + 32 * TSP;              // [32][TSP] Re(eta)
-    float* sw = et + 32 * TSP;              // [CPW][2][TS]: s row, w row
+    float* sw = et + 32 * TSP;              // [CPW][3][TS]: s row, w row, d silu(u)/du row
 
     float hr[SPT], hi[SPT];     // state h_t (normalised), walking backwards
     float er[SPT], ei[SPT];     // exp(-i theta_{t+1}) eta_{t+1}
@@ -536,33 +562,40 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
             const int slen = min(TS, tlen - sbeg);
             const int nq = (slen + 3) >> 2;
 
-            // pre-pass: s = dt silu(u), w = gy silu(z)
+            // pre-pass: every activation of the sub-block once.  s = dt silu(u), w = gy silu(z) feed the scan;
+            // silu(u) and d silu(z)/dz replace the u and z rows, d silu(u)/du gets a row of its own.
 #pragma unroll
             for (int it = 0; it < C::ITERS; ++it) {
                 const int e0 = (lane + 32 * it) * VW;
                 const int cc = e0 / TS, t = e0 % TS;
                 if (t < slen) {
                     const int o = sbeg + t;
-                    Vec<VW> u, d, z, g;
+                    Vec<VW> u, d, z, g, gu;
                     u.ld(aux + (cc * AUX + 0) * T + o);
                     d.ld(aux + (cc * AUX + 1) * T + o);
                     z.ld(aux + (cc * AUX + 2) * T + o);
                     g.ld(aux + (cc * AUX + 3) * T + o);
 #pragma unroll
                     for (int e = 0; e < VW; ++e) {
-                        d.v[e] *= siluf_(u.v[e]);
-                        g.v[e] *= siluf_(z.v[e]);
+                        float gz;
+                        u.v[e] = silu_and_grad(u.v[e], gu.v[e]);
+                        d.v[e] *= u.v[e];
+                        g.v[e] *= silu_and_grad(z.v[e], gz);
+                        z.v[e] = gz;
                     }
-                    d.st(sw + (cc * 2 + 0) * TS + t);
-                    g.st(sw + (cc * 2 + 1) * TS + t);
+                    u.st(aux + (cc * AUX + 0) * T + o);
+                    z.st(aux + (cc * AUX + 2) * T + o);
+                    d.st(sw + (cc * 3 + 0) * TS + t);
+                    g.st(sw + (cc * 3 + 1) * TS + t);
+                    gu.st(sw + (cc * 3 + 2) * TS + t);
                 }
             }
             __syncwarp();
 
             // reverse scan
-            for (int q = nq - 1; q >= 0; --q) {
-                const float4 s4 = ld_shared_f4(sw + (c * 2 + 0) * TS + 4 * q);
-                const float4 w4 = ld_shared_f4(sw + (c * 2 + 1) * TS + 4 * q);
+            auto quad = [&](const int q) {
+                const float4 s4 = ld_shared_f4(sw + (c * 3 + 0) * TS + 4 * q);
+                const float4 w4 = ld_shared_f4(sw + (c * 3 + 1) * TS + 4 * q);
                 const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
                 const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
                 float pacc[4], eacc[4];
@@ -615,6 +648,12 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
                 }
                 st_shared_f4(pt + lane * TSP + 4 * q, make_float4(pacc[0], pacc[1], pacc[2], pacc[3]));
                 st_shared_f4(et + lane * TSP + 4 * q, make_float4(eacc[0], eacc[1], eacc[2], eacc[3]));
+            };
+            if (ASYNC && slen == TS) {
+#pragma unroll
+                for (int q = TS / 4 - 1; q >= 0; --q) quad(q);
+            } else {
+                for (int q = nq - 1; q >= 0; --q) quad(q);
             }
             __syncwarp();
 
@@ -624,33 +663,31 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
                 const int e0 = (lane + 32 * it) * VW;
                 const int cc = e0 / TS, t = e0 % TS;
                 if (t < slen && cc < nvalid) {
-                    Vec<VW> P, E, u, d, z, g, du, ddt, dz;
+                    Vec<VW> P, E, v, d, gz, g, w, gu, du, ddt, dz;
+                    P.ld(pt + cc * NL * TSP + t);
+                    E.ld(et + cc * NL * TSP + t);
 #pragma unroll
-                    for (int e = 0; e < VW; ++e) P.v[e] = E.v[e] = 0.f;
-#pragma unroll
-                    for (int rr = 0; rr < NL; ++rr) {
+                    for (int rr = 1; rr < NL; ++rr) {
                         Vec<VW> a, b;
                         a.ld(pt + (cc * NL + rr) * TSP + t);
                         b.ld(et + (cc * NL + rr) * TSP + t);
-#pragma unroll
-                        for (int e = 0; e < VW; ++e) { P.v[e] += a.v[e]; E.v[e] += b.v[e]; }
+                        P.add(a);
+                        E.add(b);
                     }
                     const int o = sbeg + t;
-                    u.ld(aux + (cc * AUX + 0) * T + o);
+                    v.ld(aux + (cc * AUX + 0) * T + o);       // silu(u)
                     d.ld(aux + (cc * AUX + 1) * T + o);
-                    z.ld(aux + (cc * AUX + 2) * T + o);
+                    gz.ld(aux + (cc * AUX + 2) * T + o);      // d silu(z)/dz
                     g.ld(aux + (cc * AUX + 3) * T + o);
+                    w.ld(sw + (cc * 3 + 1) * TS + t);         // gy silu(z)
+                    gu.ld(sw + (cc * 3 + 2) * TS + t);
                     const float dv = dval[it];
 #pragma unroll
                     for (int e = 0; e < VW; ++e) {
-                        float gu, gz;
-                        const float v = silu_and_grad(u.v[e], gu);
-                        const float gg = silu_and_grad(z.v[e], gz);
-                        const float w = g.v[e] * gg;
-                        dz.v[e] = g.v[e] * fmaf(dv, v, P.v[e]) * gz;
-                        ddt.v[e] = E.v[e] * v;
-                        du.v[e] = fmaf(E.v[e], d.v[e], w * dv) * gu;
-                        if (ASYNC || t + e < slen) dacc[it] = fmaf(w, v, dacc[it]);
+                        dz.v[e] = g.v[e] * fmaf(dv, v.v[e], P.v[e]) * gz.v[e];
+                        ddt.v[e] = E.v[e] * v.v[e];
+                        du.v[e] = fmaf(E.v[e], d.v[e], w.v[e] * dv) * gu.v[e];
+                        if (ASYNC || t + e < slen) dacc[it] = fmaf(w.v[e], v.v[e], dacc[it]);
                     }
                     const long long off = (ch0 + cc) * p.ld_row + t0 + o;
                     if (ASYNC) {
@@ -673,15 +710,23 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
 
         // dtheta leaves the stage: coalesced 16-byte stores, same piece-to-lane map as the loads
         if (ASYNC) {
+            constexpr int CPR = C::CHUNKS_PER_ROW, RPI = 32 / CPR;
+            const int col = lane % CPR;
+            const float* src0 = th + (lane / CPR) * TP + col * 4;
+            float* dst0 = dtheta_warp + t0;
+            if (nvalid == C::CPW && N == NL * SPT && tlen == T) {      // whole tile, every row real: no per-piece test
 #pragma unroll
-            for (int i = 0; i < C::NCH_THETA; ++i) {
-                const int id = i * 32 + lane;
-                const int slot = id / C::CHUNKS_PER_ROW, col = id % C::CHUNKS_PER_ROW;
-                const int k = slot / 32, w = slot % 32;
-                const bool real_row = (w / NL) < nvalid && ((w % NL) + k * NL) < N;
-                if (real_row && col * 4 < tlen)
-                    *reinterpret_cast<float4*>(dtheta_warp + map.theta_off[i] + t0) =
-                        ld_shared_f4(th + slot * TP + col * 4);
+                for (int i = 0; i < C::NCH_THETA; ++i)
+                    *reinterpret_cast<float4*>(dst0 + map.theta_off[i]) = ld_shared_f4(src0 + i * RPI * TP);
+            } else {
+#pragma unroll
+                for (int i = 0; i < C::NCH_THETA; ++i) {
+                    const int slot = i * RPI + lane / CPR;
+                    const int k = slot / 32, w = slot % 32;
+                    const bool real_row = (w / NL) < nvalid && ((w % NL) + k * NL) < N;
+                    if (real_row && col * 4 < tlen)
+                        *reinterpret_cast<float4*>(dst0 + map.theta_off[i]) = ld_shared_f4(src0 + i * RPI * TP);
+                }
             }
             __syncwarp();
             const int nr = r + STAGES;
@@ -920,8 +965,12 @@ cudaError_t launch_scan_unitary_fwd(const ScanFwdParams& p_, cudaStream_t stream
         if (o.variant == 1) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 4>>(p, async, fast, stream);
         if (o.variant == 2) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 4>>(p, async, fast, stream);
         if (o.variant == 3) return launch_fwd_sel<FwdCfg<16, 1, 32, 3, 4>>(p, async, fast, stream);
-        if (o.variant == 4) return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 1>>(p, async, fast, stream);
-        if (o.variant == 5) return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 2>>(p, async, fast, stream);
+        if (o.variant == 4) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 2>>(p, async, fast, stream);
+        if (o.variant == 5) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 1>>(p, async, fast, stream);
+        if (o.variant == 6) return launch_fwd_sel<FwdCfg<4, 4, 32, 2, 1>>(p, async, fast, stream);
+        if (o.variant == 7) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 1>>(p, async, fast, stream);
+        if (o.variant == 8) return launch_fwd_sel<FwdCfg<8, 2, 16, 2, 2>>(p, async, fast, stream);
+        if (o.variant == 9) return launch_fwd_sel<FwdCfg<8, 2, 16, 3, 2>>(p, async, fast, stream);
         return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 4>>(p, async, fast, stream);
     }
     if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 32, 2, 4>>(p, async, fast, stream);
@@ -949,8 +998,9 @@ cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p_, cudaStream_t stream
         if (o.variant == 1) return launch_bwd_sel<BwdCfg<8, 2, 32, 32, 2, 2>>(p, async, fast, stream);
         if (o.variant == 2) return launch_bwd_sel<BwdCfg<16, 1, 64, 32, 2, 2>>(p, async, fast, stream);
         if (o.variant == 3) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 3, 2>>(p, async, fast, stream);
-        if (o.variant == 4) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 2>>(p, async, fast, stream);
-        if (o.variant == 5) return launch_bwd_sel<BwdCfg<16, 1, 32, 16, 2, 1>>(p, async, fast, stream);
+        if (o.variant == 8) return launch_bwd_sel<BwdCfg<8, 2, 16, 16, 2, 1>>(p, async, fast, stream);
+        if (o.variant == 9) return launch_bwd_sel<BwdCfg<8, 2, 16, 16, 3, 1>>(p, async, fast, stream);
+
         // one-warp blocks: a finished warp is replaced at once (measured 9.55 ms against 10.2 ms with two-warp blocks)
         return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 1>>(p, async, fast, stream);
     }
