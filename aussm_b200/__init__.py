@@ -11,6 +11,7 @@ from .ops import (device_status, install_as_extension_cpp, scan_unitary, ssm_ada
 __version__ = "0.1.0"
 from .s6 import selective_scan_fn
 from .variants import project, scan_complex, ssm_adaptive_complex, ssm_adaptive_preal
+from .host import HostBatchStep
 
-__all__ = ["ops", "selective_scan_fn", "scan_complex", "project", "ssm_adaptive_complex", "ssm_adaptive_preal", "ssm_adaptive_interface", "ssm_adaptive_unitary", "scan_unitary", "install_as_extension_cpp",
+__all__ = ["ops", "HostBatchStep", "selective_scan_fn", "scan_complex", "project", "ssm_adaptive_complex", "ssm_adaptive_preal", "ssm_adaptive_interface", "ssm_adaptive_unitary", "scan_unitary", "install_as_extension_cpp",
            "device_status"]

@@ -38,6 +38,9 @@ SIGNATURES = {
     "aussm_b200_selective_scan_bwd": (_I, [_P] * 9 + [_I] + [_P] * 9 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_unitary_fwd": (_I, [_P] * 15 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_unitary_bwd": (_I, [_P] * 29 + [_I] * 4 + [_P, _Z, _P]),
+    "aussm_b200_unitary_keep_bytes": (_Z, [_I] * 4),
+    "aussm_b200_unitary_fwd_keep": (_I, [_P] * 15 + [_I] * 4 + [_P, _Z, _P, _Z, _P]),
+    "aussm_b200_unitary_bwd_kept": (_I, [_P] * 29 + [_I] * 4 + [_P, _Z, _P, _Z, _P]),
 }
 
 _lib = None

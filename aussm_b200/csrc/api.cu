@@ -93,6 +93,21 @@ Plan make_plan(int B, int D, int N, int L) {
     return p;
 }
 
+size_t keep_bytes_of(const Plan& pl, int L) {
+    const size_t nwin = (size_t)((L + pl.window - 1) / pl.window);
+    return align_up(nwin * (size_t)pl.rows * pl.ldw * sizeof(float), 256);
+}
+
+bool keep_ok(const char* who, const void* keep, size_t keep_bytes, const Plan& pl, int L) {
+    if (!keep) return true;
+    const size_t need = keep_bytes_of(pl, L);
+    if (keep_bytes < need || (reinterpret_cast<uintptr_t>(keep) & 255u)) {
+        set_error("%s: phase buffer of %zu bytes (256-byte aligned) required, got %zu", who, need, keep_bytes);
+        return false;
+    }
+    return true;
+}
+
 struct OpArgs {
     const float *u, *dt, *x, *x_bias, *B_r, *B_theta, *C_r, *C_theta, *Dskip, *z;
     int B, D, N, L;
@@ -100,8 +115,11 @@ struct OpArgs {
 
 // Forward over all windows.  y == nullptr: state only.  The final state goes
 // to (out_re, out_im), which may be the workspace pair itself.
+// keep != nullptr: every window's phases go to their own slice of keep
+// (window w at keep + w * rows * ldw) instead of the one window of the workspace.
 int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, float* y, float* out_re,
-                    float* out_im, char* ws, const Plan& pl, ProjScratch& ps, cudaStream_t stream) {
+                    float* out_im, char* ws, const Plan& pl, ProjScratch& ps, cudaStream_t stream,
+                    float* keep = nullptr) {
     float* theta_w = reinterpret_cast<float*>(ws + pl.off_theta);
     float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
     float* cur_im = cur_re + pl.rows;
@@ -110,6 +128,7 @@ int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, flo
         const long long t0 = (long long)w * pl.window;
         const int tl = (int)std::min<long long>(pl.window, a.L - t0);
         const ProjDims pd = {a.B, a.D, a.N, a.L, pl.ldw, t0, tl};
+        if (keep) theta_w = keep + (size_t)w * pl.rows * pl.ldw;
         if (int rc = proj_theta(pd, a.x, a.u, theta_w, ps, stream)) return rc;
         const bool last = (w == nwin - 1);
         ScanFwdParams sp = {};
@@ -285,11 +304,11 @@ size_t aussm_b200_unitary_workspace_bytes(int B, int D, int N, int L) {
     return make_plan(B, D, N, L).total;
 }
 
-int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, const float* x_bias, const float* B_r,
-                           const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
-                           const float* z, const float* h0_re, const float* h0_im, float* y, float* h1_re,
-                           float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
-                           aussm_stream_t stream) {
+static int unitary_fwd_impl(const float* u, const float* dt, const float* x, const float* x_bias, const float* B_r,
+                            const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                            const float* z, const float* h0_re, const float* h0_im, float* y, float* h1_re,
+                            float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                            aussm_stream_t stream, float* keep, size_t keep_bytes) {
     if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
     if (!u || !dt || !x || !x_bias || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !z || !y) {
         set_error("unitary_fwd: null input or output pointer");
@@ -305,6 +324,7 @@ int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, cons
                   workspace_bytes);
         return AUSSM_EWORKSPACE;
     }
+    if (!keep_ok("unitary_fwd_keep", keep, keep_bytes, pl, L)) return AUSSM_EWORKSPACE;
     char* ws = static_cast<char*>(workspace);
     float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
     const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
@@ -312,17 +332,44 @@ int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, cons
     proj_scratch_bind(ps, reinterpret_cast<float*>(ws + pl.off_proj), B, D, N, pl.ldw);
     if (int rc = proj_begin(B, D, N, L, pl.ldw, x, u, ps, (cudaStream_t)stream)) return rc;
     return run_unitary_fwd(a, h0_re, h0_im, y, h1_re ? h1_re : cur_re, h1_im ? h1_im : cur_re + pl.rows, ws, pl, ps,
-                           (cudaStream_t)stream);
+                           (cudaStream_t)stream, keep);
 }
 
-int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
-                           const float* dt, const float* x, const float* x_bias, const float* B_r,
+int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, const float* x_bias, const float* B_r,
                            const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
-                           const float* z, const float* h0_re, const float* h0_im, const float* h1_re,
-                           const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
-                           float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
-                           float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
-                           aussm_stream_t stream_) {
+                           const float* z, const float* h0_re, const float* h0_im, float* y, float* h1_re,
+                           float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                           aussm_stream_t stream) {
+    return unitary_fwd_impl(u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, h0_re, h0_im, y, h1_re, h1_im, B,
+                            D, N, L, workspace, workspace_bytes, stream, nullptr, 0);
+}
+
+size_t aussm_b200_unitary_keep_bytes(int B, int D, int N, int L) {
+    if (B <= 0 || D <= 0 || N <= 0 || L <= 0) return 0;
+    return keep_bytes_of(make_plan(B, D, N, L), L);
+}
+
+int aussm_b200_unitary_fwd_keep(const float* u, const float* dt, const float* x, const float* x_bias,
+                                const float* B_r, const float* B_theta, const float* C_r, const float* C_theta,
+                                const float* Dskip, const float* z, const float* h0_re, const float* h0_im, float* y,
+                                float* h1_re, float* h1_im, int B, int D, int N, int L, void* workspace,
+                                size_t workspace_bytes, void* theta_keep, size_t keep_bytes, aussm_stream_t stream) {
+    if (!theta_keep) {
+        set_error("unitary_fwd_keep: null phase buffer");
+        return AUSSM_EINVAL;
+    }
+    return unitary_fwd_impl(u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, h0_re, h0_im, y, h1_re, h1_im, B,
+                            D, N, L, workspace, workspace_bytes, stream, static_cast<float*>(theta_keep), keep_bytes);
+}
+
+static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
+                            const float* dt, const float* x, const float* x_bias, const float* B_r,
+                            const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                            const float* z, const float* h0_re, const float* h0_im, const float* h1_re,
+                            const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
+                            float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
+                            float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                            aussm_stream_t stream_, float* keep, size_t keep_bytes) {
     if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
     if (!grad_y || !u || !dt || !x || !x_bias || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !z || !du ||
         !ddt || !dx || !dx_bias || !dB_r || !dB_theta || !dC_r || !dC_theta || !dD || !dz) {
@@ -339,6 +386,11 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
         set_error("unitary_bwd: workspace of %zu bytes (256-byte aligned) required, got %zu", pl.total,
                   workspace_bytes);
         return AUSSM_EWORKSPACE;
+    }
+    if (!keep_ok("unitary_bwd_kept", keep, keep_bytes, pl, L)) return AUSSM_EWORKSPACE;
+    if (keep && !h1_re) {
+        set_error("unitary_bwd_kept: the final state of the forward call is required with kept phases");
+        return AUSSM_EINVAL;
     }
     cudaStream_t stream = (cudaStream_t)stream_;
     char* ws = static_cast<char*>(workspace);
@@ -372,7 +424,12 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
         const bool first = (w == nwin - 1);   // first processed = last in time
         const bool final_ = (w == 0);
         const ProjDims pd = {B, D, N, L, pl.ldw, t0, tl};
-        if (int rc = proj_theta(pd, x, u, theta_w, ps, stream)) return rc;
+        if (keep) {
+            theta_w = keep + (size_t)w * pl.rows * pl.ldw;    // phases of the forward call; dtheta replaces them
+            if (int rc = proj_split_u(pd, u, ps, stream)) return rc;
+        } else if (int rc = proj_theta(pd, x, u, theta_w, ps, stream)) {
+            return rc;
+        }
         ScanBwdParams p = {};
         p.theta = theta_w; p.theta_bias = x_bias;
         p.u = u + t0; p.dt = dt + t0; p.z = z + t0; p.gy = grad_y + t0;
@@ -403,6 +460,37 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
     cudaError_t e = launch_reduce_param_grads(r, stream);
     if (e != cudaSuccess) return cuda_fail(e, "parameter-gradient reduction launch");
     return AUSSM_OK;
+}
+
+int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
+                           const float* dt, const float* x, const float* x_bias, const float* B_r,
+                           const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                           const float* z, const float* h0_re, const float* h0_im, const float* h1_re,
+                           const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
+                           float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
+                           float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                           aussm_stream_t stream) {
+    return unitary_bwd_impl(grad_y, gh1_re, gh1_im, u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, h0_re,
+                            h0_im, h1_re, h1_im, du, ddt, dx, dx_bias, dB_r, dB_theta, dC_r, dC_theta, dD, dz, dh0_re,
+                            dh0_im, B, D, N, L, workspace, workspace_bytes, stream, nullptr, 0);
+}
+
+int aussm_b200_unitary_bwd_kept(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
+                                const float* dt, const float* x, const float* x_bias, const float* B_r,
+                                const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                                const float* z, const float* h0_re, const float* h0_im, const float* h1_re,
+                                const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
+                                float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
+                                float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                                void* theta_keep, size_t keep_bytes, aussm_stream_t stream) {
+    if (!theta_keep) {
+        set_error("unitary_bwd_kept: null phase buffer");
+        return AUSSM_EINVAL;
+    }
+    return unitary_bwd_impl(grad_y, gh1_re, gh1_im, u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, h0_re,
+                            h0_im, h1_re, h1_im, du, ddt, dx, dx_bias, dB_r, dB_theta, dC_r, dC_theta, dD, dz, dh0_re,
+                            dh0_im, B, D, N, L, workspace, workspace_bytes, stream, static_cast<float*>(theta_keep),
+                            keep_bytes);
 }
 
 }  // extern "C"

@@ -134,14 +134,18 @@ int proj_begin(int B, int D, int N, long long L, long long ldw, const float* x, 
     return AUSSM_OK;
 }
 
+int proj_split_u(const ProjDims& d, const float* u, ProjScratch& s, cudaStream_t stream) {
+    if (!s.use_tensor_cores) return AUSSM_OK;
+    // split this window of u: rows r (D of them per batch entry), tl columns
+    return split_tf32(u + d.t0, d.L, (long long)d.D * d.L, s.u_hi, s.u_lo, d.ldw, (long long)d.D * d.ldw, d.D, d.tl,
+                      d.B, stream);
+}
+
 int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, ProjScratch& s,
                cudaStream_t stream) {
     if (!s.use_tensor_cores) return lib_theta(d, x, u, theta_w, stream);
     const int M = d.D * d.N;
-    // split this window of u: rows r (D of them per batch entry), tl columns
-    if (int rc = split_tf32(u + d.t0, d.L, (long long)d.D * d.L, s.u_hi, s.u_lo, d.ldw, (long long)d.D * d.ldw, d.D,
-                            d.tl, d.B, stream))
-        return rc;
+    if (int rc = proj_split_u(d, u, s, stream)) return rc;
     // theta_w[b] (M x tl) = x (M x D, K-major) * u_b (D x tl: K rows, N contiguous -> MN-major)
     const SplitOperand A = {s.x_hi, s.x_lo, 0, d.D, 0};
     const SplitOperand Bop = {s.u_hi, s.u_lo, 1, d.ldw, (long long)d.D * d.ldw};

@@ -43,6 +43,8 @@ int proj_begin(int B, int D, int N, long long L, long long ldw, const float* x, 
                cudaStream_t stream);
 
 // returns 0 or a negative AUSSM_E* code (message set)
+// TF32 parts of the current window of u (proj_theta does this itself; proj_adjoints expects it done).
+int proj_split_u(const ProjDims& d, const float* u, ProjScratch& s, cudaStream_t stream);
 int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, ProjScratch& s,
                cudaStream_t stream);
 // dx and du from dtheta_w; requires proj_theta() to have run on the same window (it leaves u's split behind)

@@ -1,0 +1,109 @@
+"""Forward + backward of the adaptive unitary operator for a batch that lives in pinned HOST memory.
+
+The operator is independent across batch entries (only the parameter gradients sum over the batch), so a batch
+that arrives from the host does not have to be resident on the device as a whole: ``HostBatchStep`` cuts it into
+chunks of a few batch entries and runs three CUDA streams as a pipeline,
+
+    copy-in stream   host -> device of chunk c+1 (u, dt, z, grad_y)
+    compute stream   ssm_adaptive_interface forward and backward of chunk c (parameter gradients accumulate)
+    copy-out stream  device -> host of chunk c-1 (y, du, ddt, dz)
+
+with two sets of device buffers, so that the PCIe transfers of one chunk hide behind the arithmetic of another.
+The result is the same as one ``ssm_adaptive_interface`` call on the whole batch followed by ``backward`` (the
+parameter gradients are summed chunk by chunk in a fixed order, so they are reproducible, but the order of that
+sum differs from the single call's).
+
+There is no counterpart in the reference, which keeps its batches on the device
+(extension-cpp/extension_cpp/ops.py:28-93 is the call this wraps).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+from torch import Tensor
+
+from . import ops
+
+__all__ = ["HostBatchStep"]
+
+_SEQ = ("u", "dt", "z", "gy")                    # (b, d, l) tensors that travel per chunk
+_PARAMS = ("x", "x_bias", "B", "C", "D")
+
+
+class HostBatchStep:
+    """Pipelined forward+backward over a host-resident batch.
+
+    ``step(inputs, outputs)``: ``inputs`` maps ``u, dt, z, gy`` to pinned float32 host tensors ``(b, d, l)`` and
+    ``x, x_bias, B, C, D`` to the parameters (host or device); ``outputs`` maps ``y, u, dt, z`` to pinned host
+    tensors that receive the output and the gradients of ``u, dt, z``, and ``x, x_bias, B, C, D`` to host tensors
+    that receive the parameter gradients.  The call returns after queueing everything; the caller's current
+    stream waits for the last copy, so a synchronize (or an event recorded on it) covers the whole step.
+    """
+
+    def __init__(self, device, chunk: Optional[int] = None):
+        self.device = torch.device(device)
+        self.chunk = chunk
+        self.s_in = torch.cuda.Stream(self.device)
+        self.s_cmp = torch.cuda.Stream(self.device)
+        self.s_out = torch.cuda.Stream(self.device)
+        self._bufs = None
+        self._shape = None
+
+    def _prepare(self, b, d, l, chunk):
+        key = (b, d, l, chunk)
+        if self._shape == key:
+            return
+        self._shape = key
+        mk = lambda: torch.empty(chunk, d, l, device=self.device, dtype=torch.float32)
+        self._bufs = [{k: mk() for k in _SEQ} for _ in range(2)]
+
+    def step(self, inputs: Dict[str, Tensor], outputs: Dict[str, Tensor]) -> None:
+        u = inputs["u"]
+        b, d, l = u.shape
+        chunk = self.chunk or max(1, b // 8)
+        self._prepare(b, d, l, chunk)
+        for k in _SEQ:
+            if not inputs[k].is_pinned():
+                raise RuntimeError(f"HostBatchStep: input '{k}' must be in pinned host memory")
+        cur = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_cmp, self.s_out):
+            s.wait_stream(cur)
+
+        with torch.cuda.stream(self.s_cmp):
+            params = [inputs[k].to(self.device, non_blocking=True).detach().requires_grad_(True) for k in _PARAMS]
+
+        nchunks = (b + chunk - 1) // chunk
+        in_ready = [None, None]       # copy-in of the chunk in buffer set i is complete
+        in_free = [None, None]        # the compute stream no longer reads buffer set i
+        for c in range(nchunks):
+            lo, hi = c * chunk, min(b, (c + 1) * chunk)
+            i = c % 2
+            buf = self._bufs[i]
+            with torch.cuda.stream(self.s_in):
+                if in_free[i] is not None:
+                    self.s_in.wait_event(in_free[i])
+                for k in _SEQ:
+                    buf[k][: hi - lo].copy_(inputs[k][lo:hi], non_blocking=True)
+                in_ready[i] = self.s_in.record_event()
+            with torch.cuda.stream(self.s_cmp):
+                self.s_cmp.wait_event(in_ready[i])
+                leaves = [buf[k][: hi - lo].detach().requires_grad_(True) for k in ("u", "dt", "z")]
+                y = ops.ssm_adaptive_interface(leaves[0], leaves[1], params[0], params[1], params[2], params[3],
+                                               params[4], leaves[2], unitary=True)
+                y.backward(buf["gy"][: hi - lo])
+                res = {"y": y.detach(), "u": leaves[0].grad, "dt": leaves[1].grad, "z": leaves[2].grad}
+                done = self.s_cmp.record_event()
+                in_free[i] = done
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(done)
+                for k, t in res.items():
+                    t.record_stream(self.s_out)
+                    outputs[k][lo:hi].copy_(t, non_blocking=True)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_stream(self.s_cmp)
+            for k, p in zip(_PARAMS, params):
+                p.grad.record_stream(self.s_out)
+                outputs[k].copy_(p.grad, non_blocking=True)
+        cur.wait_stream(self.s_out)
+        cur.wait_stream(self.s_in)

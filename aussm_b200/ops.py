@@ -110,7 +110,7 @@ def _unitary_forward(u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h
 
 
 def _unitary_backward(grad_y, g_re, g_im, u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h_im,
-                      final_state=None):
+                      final_state=None, keep=None):
     (b, d, n, l, u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h_im) = _check_op_inputs(
         u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h_im)
     lib = _lib.load()
@@ -139,11 +139,14 @@ def _unitary_backward(grad_y, g_re, g_im, u, dt, x, x_bias, B_r, B_theta, C_r, C
     with torch.cuda.device(u.device):
         nbytes = lib.aussm_b200_unitary_workspace_bytes(b, d, n, l)
         ws = _workspace(nbytes, u.device)
-        rc = lib.aussm_b200_unitary_bwd(
-            _ptr(grad_y), _ptr(g_re), _ptr(g_im), _ptr(u), _ptr(dt), _ptr(x), _ptr(x_bias), _ptr(B_r),
-            _ptr(B_theta), _ptr(C_r), _ptr(C_theta), _ptr(D), _ptr(z), _ptr(h_re), _ptr(h_im), _ptr(f_re),
-            _ptr(f_im), _ptr(du), _ptr(ddt), _ptr(dx), _ptr(dxb), _ptr(dBr), _ptr(dBt), _ptr(dCr), _ptr(dCt),
-            _ptr(dD), _ptr(dz), _ptr(dh_re), _ptr(dh_im), b, d, n, l, _ptr(ws), ws.numel(), _stream(u))
+        args = (_ptr(grad_y), _ptr(g_re), _ptr(g_im), _ptr(u), _ptr(dt), _ptr(x), _ptr(x_bias), _ptr(B_r),
+                _ptr(B_theta), _ptr(C_r), _ptr(C_theta), _ptr(D), _ptr(z), _ptr(h_re), _ptr(h_im), _ptr(f_re),
+                _ptr(f_im), _ptr(du), _ptr(ddt), _ptr(dx), _ptr(dxb), _ptr(dBr), _ptr(dBt), _ptr(dCr), _ptr(dCt),
+                _ptr(dD), _ptr(dz), _ptr(dh_re), _ptr(dh_im), b, d, n, l, _ptr(ws), ws.numel())
+        if keep is not None:
+            rc = lib.aussm_b200_unitary_bwd_kept(*args, _ptr(keep), keep.numel(), _stream(u))
+        else:
+            rc = lib.aussm_b200_unitary_bwd(*args, _stream(u))
     _lib.check(rc, "ssm_adaptive_backward_unitary")
     return du, ddt, dx, dxb, dBr, dBt, dCr, dCt, dD, dz, dh_re, dh_im
 
@@ -172,12 +175,65 @@ def _fake_backward(grad_y, g_re, g_im, u, dt, x, x_bias, B_r, B_theta, C_r, C_th
     return tuple(torch.empty_like(t) for t in (u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h_im))
 
 
+# Whether a differentiable call keeps its phase tensor (4*b*d*n*l bytes) for the backward pass, which then
+# skips one of the four projection GEMMs: True, False, or "auto" = when it takes at most a quarter of the
+# device memory that is free at the time of the call.  Results are bit-identical either way.
+keep_phases = "auto"
+
+
+def _want_keep(inputs, b, d, n, l) -> int:
+    """Size of the phase buffer to keep for this call, or 0 for the recomputing path."""
+    if keep_phases is False or not torch.is_grad_enabled() or not any(t.requires_grad for t in inputs):
+        return 0
+    if b == 0 or l == 0:
+        return 0
+    nbytes = _lib.load().aussm_b200_unitary_keep_bytes(b, d, n, l)
+    if keep_phases is True:
+        return nbytes
+    free, _total = torch.cuda.mem_get_info(inputs[0].device)
+    return nbytes if nbytes <= free // 4 else 0
+
+
+class _UnitaryKeep(torch.autograd.Function):
+    """extension_cpp::ssm_adaptive_unitary with the phases kept for the backward pass."""
+
+    @staticmethod
+    def forward(ctx, keep_bytes, *inputs):
+        (b, d, n, l, u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h_im) = _check_op_inputs(*inputs)
+        lib = _lib.load()
+        y, o_re, o_im = torch.empty_like(u), torch.empty_like(h_re), torch.empty_like(h_im)
+        keep = torch.empty(keep_bytes, dtype=torch.uint8, device=u.device)
+        with torch.cuda.device(u.device):
+            ws = _workspace(lib.aussm_b200_unitary_workspace_bytes(b, d, n, l), u.device)
+            rc = lib.aussm_b200_unitary_fwd_keep(
+                _ptr(u), _ptr(dt), _ptr(x), _ptr(x_bias), _ptr(B_r), _ptr(B_theta), _ptr(C_r), _ptr(C_theta),
+                _ptr(D), _ptr(z), _ptr(h_re), _ptr(h_im), _ptr(y), _ptr(o_re), _ptr(o_im), b, d, n, l, _ptr(ws),
+                ws.numel(), _ptr(keep), keep.numel(), _stream(u))
+        _lib.check(rc, "ssm_adaptive_unitary (phases kept)")
+        ctx.save_for_backward(u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h_im, o_re, o_im)
+        ctx.keep = keep
+        return y, o_re, o_im
+
+    @staticmethod
+    def backward(ctx, grad_y, g_re, g_im):
+        saved = ctx.saved_tensors
+        inputs, f_re, f_im = saved[:12], saved[12], saved[13]
+        if grad_y is None:
+            grad_y = torch.zeros_like(inputs[0])
+        keep, ctx.keep = ctx.keep, None        # the backward call overwrites the phases: usable once
+        return (None,) + tuple(_unitary_backward(grad_y, g_re, g_im, *inputs, final_state=(f_re, f_im), keep=keep))
+
+
 def ssm_adaptive_unitary(u: Tensor, dt: Tensor, x: Tensor, x_bias: Tensor, B_r: Tensor, B_theta: Tensor,
                          C_r: Tensor, C_theta: Tensor, D: Tensor, z: Tensor, prev_hidden_state_real: Tensor,
                          prev_hidden_state_imag: Tensor) -> Tuple[Tensor, Tensor, Tensor]:
     """The operator call of the reference (ops.py:97-105): returns (y, next_hid_real, next_hid_imag)."""
-    return torch.ops.extension_cpp.ssm_adaptive_unitary.default(
-        u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, prev_hidden_state_real, prev_hidden_state_imag)
+    inputs = (u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, prev_hidden_state_real, prev_hidden_state_imag)
+    if u.is_cuda and u.dim() == 3 and x.dim() == 3:
+        keep_bytes = _want_keep(inputs, u.shape[0], u.shape[1], x.shape[1], u.shape[2])
+        if keep_bytes:
+            return _UnitaryKeep.apply(keep_bytes, *inputs)
+    return torch.ops.extension_cpp.ssm_adaptive_unitary.default(*inputs)
 
 
 def _setup_context(ctx, inputs, output):

@@ -159,6 +159,31 @@ int aussm_b200_unitary_bwd(const float* grad_y, const float* gh1_re, const float
                            float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
                            aussm_stream_t stream);
 
+/* The same pair with the phases kept between forward and backward (no
+ * counterpart in the reference, whose backward recomputes every intermediate
+ * from the 12 inputs: ssm_adaptive_unitary_backward.cu:50-141).  The forward
+ * writes every window's phases into `theta_keep` (aussm_b200_unitary_keep_bytes
+ * bytes, 256-byte aligned: about 4*B*D*N*L); the backward reads them instead
+ * of running the projection again and overwrites them with their gradient, so
+ * the buffer is consumed by one backward call.  The final state h1_* of the
+ * forward call is required.  Results are bit-identical to the plain pair. */
+size_t aussm_b200_unitary_keep_bytes(int B, int D, int N, int L);
+
+int aussm_b200_unitary_fwd_keep(const float* u, const float* dt, const float* x, const float* x_bias,
+                                const float* B_r, const float* B_theta, const float* C_r, const float* C_theta,
+                                const float* Dskip, const float* z, const float* h0_re, const float* h0_im, float* y,
+                                float* h1_re, float* h1_im, int B, int D, int N, int L, void* workspace,
+                                size_t workspace_bytes, void* theta_keep, size_t keep_bytes, aussm_stream_t stream);
+
+int aussm_b200_unitary_bwd_kept(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
+                                const float* dt, const float* x, const float* x_bias, const float* B_r,
+                                const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
+                                const float* z, const float* h0_re, const float* h0_im, const float* h1_re,
+                                const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
+                                float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
+                                float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                                void* theta_keep, size_t keep_bytes, aussm_stream_t stream);
+
 /* ---- real selective scan of the Mamba block ("S6") -------------------------
  * The reference's MambaBlock calls mamba_ssm.selective_scan_fn, a third-party
  * CUDA extension that is not part of the reference tree
