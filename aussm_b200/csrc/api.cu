@@ -289,12 +289,26 @@ int aussm_b200_gemm_tf32x3(const float* A, int a_mn_major, int a_batched, const 
     float* a_lo = a_hi + (size_t)a_rows * a_cols * na;
     float* b_hi = a_lo + (size_t)a_rows * a_cols * na;
     float* b_lo = b_hi + (size_t)b_rows * b_cols * nb;
-    if (int rc = split_tf32(A, a_cols, a_rows * a_cols, a_hi, a_lo, a_cols, a_rows * a_cols, a_rows, a_cols, na, stream))
-        return rc;
-    if (int rc = split_tf32(Bm, b_cols, b_rows * b_cols, b_hi, b_lo, b_cols, b_rows * b_cols, b_rows, b_cols, nb, stream))
-        return rc;
-    const SplitOperand sa = {a_hi, a_lo, a_mn_major, a_cols, a_batched ? a_rows * a_cols : 0};
-    const SplitOperand sb = {b_hi, b_lo, b_mn_major, b_cols, b_batched ? b_rows * b_cols : 0};
+    // FP16 parts (half the bytes, twice the tensor-core rate) when every pitch is a multiple of 8, else TF32 parts
+    const bool half = gemm_backend() == 0 && a_cols % 8 == 0 && b_cols % 8 == 0;
+    unsigned* amax = reinterpret_cast<unsigned*>(b_lo + (size_t)b_rows * b_cols * nb);   // in the spare 1 KiB
+    if (half) {
+        if (int rc = split_f16(A, a_cols, a_rows * a_cols, a_hi, a_lo, a_cols, a_rows * a_cols, a_rows, a_cols, na,
+                               amax + 0, stream))
+            return rc;
+        if (int rc = split_f16(Bm, b_cols, b_rows * b_cols, b_hi, b_lo, b_cols, b_rows * b_cols, b_rows, b_cols, nb,
+                               amax + 1, stream))
+            return rc;
+    } else {
+        if (int rc = split_tf32(A, a_cols, a_rows * a_cols, a_hi, a_lo, a_cols, a_rows * a_cols, a_rows, a_cols, na,
+                                stream))
+            return rc;
+        if (int rc = split_tf32(Bm, b_cols, b_rows * b_cols, b_hi, b_lo, b_cols, b_rows * b_cols, b_rows, b_cols, nb,
+                                stream))
+            return rc;
+    }
+    const SplitOperand sa = {a_hi, a_lo, a_mn_major, a_cols, a_batched ? a_rows * a_cols : 0, half ? amax + 0 : nullptr};
+    const SplitOperand sb = {b_hi, b_lo, b_mn_major, b_cols, b_batched ? b_rows * b_cols : 0, half ? amax + 1 : nullptr};
     const GemmShape shape = {M, N, K, batches, reduce_batches, beta, N, reduce_batches ? 0 : (long long)M * N};
     return gemm_tf32x3(sa, sb, C, shape, stream);
 }

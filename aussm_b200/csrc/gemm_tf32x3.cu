@@ -23,6 +23,7 @@
 #include "gemm_tf32x3.cuh"
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 #include <mutex>
@@ -35,10 +36,11 @@
 namespace aussm {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 32;          // BK floats = 128 bytes = one swizzle row
+constexpr int BM = 128, BN = 128;
+constexpr int BK_BYTES = 128;                        // one K block = one 128-byte swizzle row: 32 TF32 or 64 FP16 values
 constexpr int STAGES = 3;
-constexpr int A_TILE_BYTES = BM * BK * 4;            // 16 KB
-constexpr int B_TILE_BYTES = BN * BK * 4;            // 16 KB
+constexpr int A_TILE_BYTES = BM * BK_BYTES;          // 16 KB
+constexpr int B_TILE_BYTES = BN * BK_BYTES;          // 16 KB
 constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // hi + lo of both operands: 64 KB
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + slack for 1024-byte alignment
 // Tensor-memory accumulation truncates instead of rounding, so a long K loop drifts (measured 3.5e-5 relative
@@ -46,7 +48,8 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + slack for
 // into one of two TMEM buffers and the epilogue warps add the finished chunk into float32 registers
 // (round-to-nearest) while the next chunk runs.  Each buffer holds two accumulators: the hi*hi products and the
 // two small cross terms, so that adding the tiny terms does not cost the big sum an extra truncation.
-constexpr int CHUNK_KB = 2;
+// FP16 parts: the scaled low part is stored times 2^LO_SHIFT (see split_f16_kernel)
+constexpr int LO_SHIFT = 11;
 constexpr int ACC_COLS = 2 * BN;                     // main + cross accumulator of one buffer
 constexpr int TMEM_COLS = 2 * ACC_COLS;              // 512: two buffers
 constexpr int EPI_WARPS = 8;                         // two per TMEM lane quarter, 64 columns each
@@ -62,7 +65,20 @@ struct GemmKernelParams {
     int b_batched;
     int beta;
     int* status;
+    const unsigned* amax_a;   // FP16 parts: bit patterns of max|a|, max|b| (the parts are scaled by a power of two)
+    const unsigned* amax_b;
 };
+
+// Power-of-two scale that brings a tensor whose largest magnitude has the bit pattern `maxbits` to about 2^14
+// (FP16 overflows at 65504), and its exact inverse.
+__host__ __device__ __forceinline__ int scale_exponent(unsigned maxbits) {
+    const int e = (int)((maxbits >> 23) & 0xffu) - 127;      // floor(log2(max)); -127 for zero / subnormal
+    int k = 14 - e;
+    if (k > 100) k = 100;
+    if (k < -100) k = -100;
+    return k;
+}
+__device__ __forceinline__ float pow2f(int k) { return __uint_as_float((unsigned)(127 + k) << 23); }
 
 // ---- PTX wrappers ---------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
@@ -93,6 +109,15 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -133,9 +158,14 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (layout_type << 61);
 }
 
-// descriptor of the kk-th K=8 slice of an operand tile
-template <int MN_MAJOR>
+// descriptor of the kk-th slice (32 bytes of K: 8 TF32 or 16 FP16 values) of an operand tile
+template <int MN_MAJOR, bool HALF>
 __device__ __forceinline__ uint64_t operand_desc(uint32_t tile_saddr, int kk) {
+    if (MN_MAJOR && HALF) {
+        // 16-bit MN-major, plain 128-byte swizzle (type 2): TMA boxes of 64 K-rows x 64 row-elements (8 KB)
+        // placed 8192 B apart along the row index, groups of 8 K-rows 1024 B apart; a K=16 slice is two groups
+        return smem_desc(tile_saddr + kk * 2048, 8192, 1024, 2);
+    }
     if (MN_MAJOR) {
         // 32-bit MN-major operands only exist in the "128-byte swizzle, 32-byte atom" layout (type 1): boxes of
         // 32 K-rows x 128 B placed 4096 B apart along the row index, groups of 4 K-rows 512 B apart; a K=8
@@ -147,15 +177,15 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t tile_saddr, int kk) {
     return smem_desc(tile_saddr + kk * 32, 16, 1024, 2);
 }
 
-// Instruction descriptor for kind::tf32, float32 accumulate: c_format=1 (bits 4-5), a/b format TF32=2
-// (bits 7-9, 10-12), a/b major (bits 15, 16), N>>3 (bits 17-22), M>>4 (bits 24-28).
-template <int A_MN, int B_MN>
+// Instruction descriptor, float32 accumulate: c_format=1 (bits 4-5), a/b format (bits 7-9, 10-12: TF32=2 for
+// kind::tf32, F16=0 for kind::f16), a/b major (bits 15, 16), N>>3 (bits 17-22), M>>4 (bits 24-28).
+template <int A_MN, int B_MN, bool HALF>
 __device__ __forceinline__ constexpr uint32_t instr_desc() {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)A_MN << 15) | ((uint32_t)B_MN << 16) |
-           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    return (1u << 4) | ((HALF ? 0u : 2u) << 7) | ((HALF ? 0u : 2u) << 10) | ((uint32_t)A_MN << 15) |
+           ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, bool HALF>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
                    const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
@@ -169,6 +199,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int zb = blockIdx.z;                                  // independent batch entry (0 when reducing)
+    constexpr int BK = HALF ? 64 : 32;                         // K values per block
+    constexpr int MNBOX = HALF ? 64 : 32;                      // row elements per MN-major TMA box
+    constexpr int MNBOX_BYTES = MNBOX * BK_BYTES;
+    constexpr int CHUNK_KB = HALF ? 1 : 2;                     // 64 K values per chunk either way
     const int kblocks = (p.K + BK - 1) / BK;
     const int total = kblocks * p.kbatches;
     const int nchunks = (total + CHUNK_KB - 1) / CHUNK_KB;
@@ -211,9 +245,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                 const int k0 = kb * BK;
                 if (A_MN) {
 #pragma unroll
-                    for (int i = 0; i < BM / 32; ++i) {
-                        tma_load_3d(a_hi + i * 4096, &mapA_hi, &full_bar[s], m0 + 32 * i, k0, ba);
-                        tma_load_3d(a_lo + i * 4096, &mapA_lo, &full_bar[s], m0 + 32 * i, k0, ba);
+                    for (int i = 0; i < BM / MNBOX; ++i) {
+                        tma_load_3d(a_hi + i * MNBOX_BYTES, &mapA_hi, &full_bar[s], m0 + MNBOX * i, k0, ba);
+                        tma_load_3d(a_lo + i * MNBOX_BYTES, &mapA_lo, &full_bar[s], m0 + MNBOX * i, k0, ba);
                     }
                 } else {
                     tma_load_3d(a_hi, &mapA_hi, &full_bar[s], k0, m0, ba);
@@ -221,9 +255,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                 }
                 if (B_MN) {
 #pragma unroll
-                    for (int i = 0; i < BN / 32; ++i) {
-                        tma_load_3d(b_hi + i * 4096, &mapB_hi, &full_bar[s], n0 + 32 * i, k0, bb);
-                        tma_load_3d(b_lo + i * 4096, &mapB_lo, &full_bar[s], n0 + 32 * i, k0, bb);
+                    for (int i = 0; i < BN / MNBOX; ++i) {
+                        tma_load_3d(b_hi + i * MNBOX_BYTES, &mapB_hi, &full_bar[s], n0 + MNBOX * i, k0, bb);
+                        tma_load_3d(b_lo + i * MNBOX_BYTES, &mapB_lo, &full_bar[s], n0 + MNBOX * i, k0, bb);
                     }
                 } else {
                     tma_load_3d(b_hi, &mapB_hi, &full_bar[s], k0, n0, bb);
@@ -234,7 +268,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer: one chunk of CHUNK_KB K-blocks per TMEM buffer ----
-            constexpr uint32_t idesc = instr_desc<A_MN, B_MN>();
+            constexpr uint32_t idesc = instr_desc<A_MN, B_MN, HALF>();
             bool ok = true;
             int it = 0;
             for (int c = 0; c < nchunks && ok; ++c) {
@@ -253,13 +287,19 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                     const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES, b_hi = st + 2 * A_TILE_BYTES,
                                    b_lo = st + 2 * A_TILE_BYTES + B_TILE_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < BK / 8; ++kk) {
-                        const uint64_t ah = operand_desc<A_MN>(a_hi, kk), al = operand_desc<A_MN>(a_lo, kk);
-                        const uint64_t bh = operand_desc<B_MN>(b_hi, kk), bl = operand_desc<B_MN>(b_lo, kk);
+                    for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
+                        const uint64_t ah = operand_desc<A_MN, HALF>(a_hi, kk), al = operand_desc<A_MN, HALF>(a_lo, kk);
+                        const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk), bl = operand_desc<B_MN, HALF>(b_lo, kk);
                         const uint32_t first = (j > 0 || kk > 0) ? 1u : 0u;
-                        umma_tf32(acc_main, ah, bh, idesc, first);
-                        umma_tf32(acc_cross, ah, bl, idesc, first);
-                        umma_tf32(acc_cross, al, bh, idesc, 1u);
+                        if (HALF) {
+                            umma_f16(acc_main, ah, bh, idesc, first);
+                            umma_f16(acc_cross, ah, bl, idesc, first);
+                            umma_f16(acc_cross, al, bh, idesc, 1u);
+                        } else {
+                            umma_tf32(acc_main, ah, bh, idesc, first);
+                            umma_tf32(acc_cross, ah, bl, idesc, first);
+                            umma_tf32(acc_cross, al, bh, idesc, 1u);
+                        }
                     }
                     umma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
                 }
@@ -273,6 +313,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
         float acc[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+        // FP16 parts carry power-of-two scales: undo them (exactly) when a chunk is added
+        float unscale_a = 1.f, unscale_b = 1.f, cross_scale = 1.f;
+        if (HALF) {
+            unscale_a = pow2f(-scale_exponent(*p.amax_a));
+            unscale_b = pow2f(-scale_exponent(*p.amax_b));
+            cross_scale = pow2f(-LO_SHIFT);
+        }
         bool ok = true;
         for (int c = 0; c < nchunks && ok; ++c) {
             const int buf = c & 1;
@@ -287,7 +334,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                     tmem_ld32(t0 + part * 32, vm);            // hi*hi
                     tmem_ld32(t0 + BN + part * 32, vc);       // hi*lo + lo*hi
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) acc[part * 32 + i] += vm[i] + vc[i];
+                    for (int i = 0; i < 32; ++i) {
+                        if (HALF) acc[part * 32 + i] += (fmaf(vc[i], cross_scale, vm[i]) * unscale_a) * unscale_b;
+                        else acc[part * 32 + i] += vm[i] + vc[i];
+                    }
                 }
             }
             tc_fence_before();
@@ -348,6 +398,58 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
     }
 }
 
+// FP16 parts.  With S = 2^k the power of two that brings max|src| to about 2^14:
+//   hi = fp16(S a),  lo = fp16((S a - hi) 2^LO_SHIFT)
+// hi carries the first 11 significant bits and lo the next 11 (stored scaled up so that it stays in FP16's
+// normal range); a*b ~ (hi_a hi_b + (hi_a lo_b + lo_a hi_b) 2^-LO_SHIFT) / (S_a S_b), as with the TF32 split.
+__global__ void __launch_bounds__(256) absmax_kernel(const float* __restrict__ src, long long ld_src,
+                                                     long long src_bs, long long rows, long long cols4,
+                                                     unsigned* __restrict__ amax) {
+    const long long b = blockIdx.z;
+    const long long total = rows * cols4;
+    float m = 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols4, c = (i % cols4) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(src + b * src_bs + r * ld_src + c);
+        m = fmaxf(fmaxf(fmaxf(m, fabsf(v.x)), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    // non-negative floats order like their bit patterns; NaN / inf would only spoil a result that is spoilt anyway
+    if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax, __float_as_uint(fminf(m, 3.0e38f)));
+}
+
+__global__ void __launch_bounds__(256) split_f16_kernel(const float* __restrict__ src, long long ld_src,
+                                                        long long src_bs, __half* __restrict__ hi,
+                                                        __half* __restrict__ lo, long long ld_dst, long long dst_bs,
+                                                        long long rows, long long cols4,
+                                                        const unsigned* __restrict__ amax) {
+    const long long b = blockIdx.z;
+    const long long total = rows * cols4;
+    const float S = pow2f(scale_exponent(*amax));
+    const float up = pow2f(LO_SHIFT);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / cols4, c = (i % cols4) * 4;
+        const float4 v = *reinterpret_cast<const float4*>(src + b * src_bs + r * ld_src + c);
+        const float a[4] = {v.x * S, v.y * S, v.z * S, v.w * S};
+        __half h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            h[e] = __float2half_rn(a[e]);
+            l[e] = __float2half_rn((a[e] - __half2float(h[e])) * up);
+        }
+        uint2 ph, pl;
+        ph.x = (uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16);
+        ph.y = (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16);
+        pl.x = (uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16);
+        pl.y = (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16);
+        *reinterpret_cast<uint2*>(hi + b * dst_bs + r * ld_dst + c) = ph;
+        *reinterpret_cast<uint2*>(lo + b * dst_bs + r * ld_dst + c) = pl;
+    }
+}
+
 // ---- host side --------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -368,7 +470,7 @@ EncodeTiledFn encode_fn() {
 
 // Tensor map of one split part: K-major -> dims (K, rows, batch), box (32, box_rows, 1);
 // MN-major -> dims (rows, K, batch), box (32, 32, 1).  Out-of-range elements read as zero.
-int make_map(CUtensorMap* map, const float* base, int mn_major, long long rows, long long K, long long ld,
+int make_map(CUtensorMap* map, const void* base, bool half, int mn_major, long long rows, long long K, long long ld,
              long long batch_stride, int batches, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
@@ -377,20 +479,22 @@ int make_map(CUtensorMap* map, const float* base, int mn_major, long long rows, 
     }
     cuuint64_t dims[3], strides[2];
     cuuint32_t box[3], estr[3] = {1, 1, 1};
+    const cuuint32_t inner = half ? 64 : 32;      // 128 bytes of the contiguous index per box row
+    const cuuint64_t esize = half ? 2 : 4;
     if (mn_major) {
         dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K;
-        box[0] = 32; box[1] = 32;
+        box[0] = inner; box[1] = inner;           // one K block of rows: 32 x 32 floats or 64 x 64 halves
     } else {
         dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows;
-        box[0] = 32; box[1] = (cuuint32_t)box_rows;
+        box[0] = inner; box[1] = (cuuint32_t)box_rows;
     }
     dims[2] = (cuuint64_t)batches;
     box[2] = 1;
-    strides[0] = (cuuint64_t)ld * 4;
-    strides[1] = (cuuint64_t)(batches > 1 ? batch_stride : (long long)dims[1] * ld) * 4;
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+    strides[0] = (cuuint64_t)ld * esize;
+    strides[1] = (cuuint64_t)(batches > 1 ? batch_stride : (long long)dims[1] * ld) * esize;
+    CUresult r = fn(map, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    (mn_major && !half) ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -401,9 +505,9 @@ int make_map(CUtensorMap* map, const float* base, int mn_major, long long rows, 
     return AUSSM_OK;
 }
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, bool HALF>
 int launch(const CUtensorMap* maps, const GemmKernelParams& kp, dim3 grid, cudaStream_t stream) {
-    auto kern = gemm_tf32x3_kernel<A_MN, B_MN>;
+    auto kern = gemm_tf32x3_kernel<A_MN, B_MN, HALF>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) {
         set_error("gemm_tf32x3: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -424,7 +528,9 @@ bool ok16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 bool gemm_tf32x3_supported(const SplitOperand& A, const SplitOperand& B, const float* C, const GemmShape& s) {
     if (s.M <= 0 || s.N <= 0 || s.K <= 0 || s.batches <= 0) return false;
-    if (A.ld % 4 || B.ld % 4 || s.ldc % 4 || A.batch_stride % 4 || B.batch_stride % 4 || s.c_batch_stride % 4)
+    if ((A.amax == nullptr) != (B.amax == nullptr)) return false;        // both operands in the same kind of parts
+    const int q = A.amax ? 8 : 4;                                        // elements per 16 bytes
+    if (A.ld % q || B.ld % q || A.batch_stride % q || B.batch_stride % q || s.ldc % 4 || s.c_batch_stride % 4)
         return false;
     if (!ok16(A.hi) || !ok16(A.lo) || !ok16(B.hi) || !ok16(B.lo) || !ok16(C)) return false;
     return encode_fn() != nullptr;
@@ -437,10 +543,11 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
     }
     alignas(64) CUtensorMap maps[4];
     const int ab = A.batch_stride != 0 ? s.batches : 1, bb = B.batch_stride != 0 ? s.batches : 1;
-    if (int rc = make_map(&maps[0], A.hi, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
-    if (int rc = make_map(&maps[1], A.lo, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
-    if (int rc = make_map(&maps[2], B.hi, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
-    if (int rc = make_map(&maps[3], B.lo, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
+    const bool half = A.amax != nullptr;
+    if (int rc = make_map(&maps[0], A.hi, half, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
+    if (int rc = make_map(&maps[1], A.lo, half, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
+    if (int rc = make_map(&maps[2], B.hi, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
+    if (int rc = make_map(&maps[3], B.lo, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
     GemmKernelParams kp;
     kp.C = C; kp.ldc = s.ldc; kp.c_batch_stride = s.c_batch_stride;
     kp.M = s.M; kp.N = s.N; kp.K = s.K;
@@ -448,14 +555,48 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
     kp.beta = s.beta;
     kp.a_batched = A.batch_stride != 0;
     kp.b_batched = B.batch_stride != 0;
+    kp.amax_a = A.amax;
+    kp.amax_b = B.amax;
     kp.status = device_status_ptr();
     if (!kp.status) {
         set_error("gemm_tf32x3: device status word unavailable");
         return AUSSM_ECUDA;
     }
     dim3 grid((s.M + BM - 1) / BM, (s.N + BN - 1) / BN, s.reduce_batches ? 1 : s.batches);
-    if (A.mn_major) return B.mn_major ? launch<1, 1>(maps, kp, grid, stream) : launch<1, 0>(maps, kp, grid, stream);
-    return B.mn_major ? launch<0, 1>(maps, kp, grid, stream) : launch<0, 0>(maps, kp, grid, stream);
+    if (half) {
+        if (A.mn_major)
+            return B.mn_major ? launch<1, 1, true>(maps, kp, grid, stream) : launch<1, 0, true>(maps, kp, grid, stream);
+        return B.mn_major ? launch<0, 1, true>(maps, kp, grid, stream) : launch<0, 0, true>(maps, kp, grid, stream);
+    }
+    if (A.mn_major)
+        return B.mn_major ? launch<1, 1, false>(maps, kp, grid, stream) : launch<1, 0, false>(maps, kp, grid, stream);
+    return B.mn_major ? launch<0, 1, false>(maps, kp, grid, stream) : launch<0, 0, false>(maps, kp, grid, stream);
+}
+
+int split_f16(const float* src, long long ld_src, long long src_batch_stride, void* hi, void* lo, long long ld_dst,
+              long long dst_batch_stride, long long rows, long long cols, int batches, unsigned* amax,
+              cudaStream_t stream) {
+    if (cols % 4 || ld_src % 4 || ld_dst % 8 || dst_batch_stride % 8 || !ok16(src) || !ok16(hi) || !ok16(lo) || !amax) {
+        set_error("split_f16: rows must be 16-byte aligned (cols=%lld ld_src=%lld ld_dst=%lld)", cols, ld_src, ld_dst);
+        return AUSSM_EINVAL;
+    }
+    const long long total = rows * (cols / 4);
+    if (total <= 0 || batches <= 0) return AUSSM_OK;
+    cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(unsigned), stream);
+    if (e == cudaSuccess) {
+        const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148 * 8);
+        absmax_kernel<<<dim3(blocks, 1, batches), 256, 0, stream>>>(src, ld_src, src_batch_stride, rows, cols / 4,
+                                                                    amax);
+        split_f16_kernel<<<dim3(std::min<unsigned>(blocks * 2, 148 * 16), 1, batches), 256, 0, stream>>>(
+            src, ld_src, src_batch_stride, static_cast<__half*>(hi), static_cast<__half*>(lo), ld_dst,
+            dst_batch_stride, rows, cols / 4, amax);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        set_error("split_f16 launch: %s", cudaGetErrorString(e));
+        return AUSSM_ECUDA;
+    }
+    return AUSSM_OK;
 }
 
 int split_tf32(const float* src, long long ld_src, long long src_batch_stride, float* hi, float* lo, long long ld_dst,

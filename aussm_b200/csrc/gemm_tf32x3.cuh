@@ -12,12 +12,19 @@ namespace aussm {
 // as [rows][K] with K contiguous; `mn_major == 1`: stored as [K][rows] with the
 // row (M or N) index contiguous.  `ld` is the pitch of the slower index in
 // floats (a multiple of 4), `batch_stride` the distance between batch entries.
+//
+// Two kinds of parts.  amax == nullptr: TF32 parts stored as floats.  amax != nullptr: FP16 parts (hi / lo point to
+// __half arrays, ld and batch_stride count halves and are multiples of 8) written by split_f16, which scales the
+// tensor by a power of two derived from its largest magnitude; `amax` points to that magnitude's bit pattern on
+// the device.  FP16 parts have the same 2 x 11 significant bits as TF32 parts but move half the bytes and run
+// at twice the tensor-core rate.
 struct SplitOperand {
-    const float* hi;
-    const float* lo;
+    const void* hi;
+    const void* lo;
     int mn_major;
     long long ld;
     long long batch_stride;
+    const unsigned* amax = nullptr;
 };
 
 struct GemmShape {
@@ -38,5 +45,10 @@ bool gemm_tf32x3_supported(const SplitOperand& A, const SplitOperand& B, const f
 // hi/lo split of a strided 2-D array (rows x cols, cols contiguous), batched
 int split_tf32(const float* src, long long ld_src, long long src_batch_stride, float* hi, float* lo, long long ld_dst,
                long long dst_batch_stride, long long rows, long long cols, int batches, cudaStream_t stream);
+
+// FP16 hi/lo split (see SplitOperand); amax is a device word that receives the bit pattern of max|src|
+int split_f16(const float* src, long long ld_src, long long src_batch_stride, void* hi, void* lo, long long ld_dst,
+              long long dst_batch_stride, long long rows, long long cols, int batches, unsigned* amax,
+              cudaStream_t stream);
 
 }  // namespace aussm

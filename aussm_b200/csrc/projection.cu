@@ -101,6 +101,7 @@ int lib_du(const ProjDims& d, const float* dtheta_w, const float* x, float* du, 
 }  // namespace
 
 void set_gemm_backend(int mode) { g_gemm_backend = mode; }
+int gemm_backend() { return g_gemm_backend; }
 
 size_t proj_scratch_floats(int B, int D, int N, long long ldw) {
     const size_t M = (size_t)D * N;
@@ -116,7 +117,9 @@ void proj_scratch_bind(ProjScratch& s, float* base, int B, int D, int N, long lo
     s.u_lo = s.u_hi + up4((size_t)B * D * ldw);
     s.dth_hi = s.u_lo + up4((size_t)B * D * ldw);
     s.dth_lo = s.dth_hi + up4((size_t)B * M * ldw);
+    s.amax = reinterpret_cast<unsigned*>(s.dth_lo + up4((size_t)B * M * ldw));   // inside the 64 spare floats
     s.use_tensor_cores = 0;
+    s.half = 0;
 }
 
 int proj_begin(int B, int D, int N, long long L, long long ldw, const float* x, const float* u, ProjScratch& s,
@@ -129,7 +132,13 @@ int proj_begin(int B, int D, int N, long long L, long long ldw, const float* x, 
     SplitOperand probe = {s.x_hi, s.x_lo, 0, D, 0};
     GemmShape shape = {D * N, 4, D, 1, 0, 0, ldw, 0};
     if (!gemm_tf32x3_supported(probe, probe, s.x_hi, shape)) return AUSSM_OK;
-    if (int rc = split_tf32(x, D, 0, s.x_hi, s.x_lo, D, 0, (long long)D * N, D, 1, stream)) return rc;
+    // FP16 parts need 16-byte rows of halves: pitches that are multiples of 8
+    s.half = (g_gemm_backend == 0 && D % 8 == 0 && ldw % 8 == 0) ? 1 : 0;
+    if (s.half) {
+        if (int rc = split_f16(x, D, 0, s.x_hi, s.x_lo, D, 0, (long long)D * N, D, 1, s.amax + 0, stream)) return rc;
+    } else {
+        if (int rc = split_tf32(x, D, 0, s.x_hi, s.x_lo, D, 0, (long long)D * N, D, 1, stream)) return rc;
+    }
     s.use_tensor_cores = 1;
     return AUSSM_OK;
 }
@@ -137,6 +146,9 @@ int proj_begin(int B, int D, int N, long long L, long long ldw, const float* x, 
 int proj_split_u(const ProjDims& d, const float* u, ProjScratch& s, cudaStream_t stream) {
     if (!s.use_tensor_cores) return AUSSM_OK;
     // split this window of u: rows r (D of them per batch entry), tl columns
+    if (s.half)
+        return split_f16(u + d.t0, d.L, (long long)d.D * d.L, s.u_hi, s.u_lo, d.ldw, (long long)d.D * d.ldw, d.D, d.tl,
+                         d.B, s.amax + 1, stream);
     return split_tf32(u + d.t0, d.L, (long long)d.D * d.L, s.u_hi, s.u_lo, d.ldw, (long long)d.D * d.ldw, d.D, d.tl,
                       d.B, stream);
 }
@@ -147,8 +159,8 @@ int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w
     const int M = d.D * d.N;
     if (int rc = proj_split_u(d, u, s, stream)) return rc;
     // theta_w[b] (M x tl) = x (M x D, K-major) * u_b (D x tl: K rows, N contiguous -> MN-major)
-    const SplitOperand A = {s.x_hi, s.x_lo, 0, d.D, 0};
-    const SplitOperand Bop = {s.u_hi, s.u_lo, 1, d.ldw, (long long)d.D * d.ldw};
+    const SplitOperand A = {s.x_hi, s.x_lo, 0, d.D, 0, s.half ? s.amax + 0 : nullptr};
+    const SplitOperand Bop = {s.u_hi, s.u_lo, 1, d.ldw, (long long)d.D * d.ldw, s.half ? s.amax + 1 : nullptr};
     const GemmShape shape = {M, d.tl, d.D, d.B, 0, 0, d.ldw, (long long)M * d.ldw};
     return gemm_tf32x3(A, Bop, theta_w, shape, stream);
 }
@@ -160,21 +172,29 @@ int proj_adjoints(const ProjDims& d, const float* dtheta_w, const float* x, cons
         return lib_du(d, dtheta_w, x, du, stream);
     }
     const int M = d.D * d.N;
-    if (int rc = split_tf32(dtheta_w, d.ldw, (long long)M * d.ldw, s.dth_hi, s.dth_lo, d.ldw, (long long)M * d.ldw, M,
-                            d.tl, d.B, stream))
+    if (s.half) {
+        if (int rc = split_f16(dtheta_w, d.ldw, (long long)M * d.ldw, s.dth_hi, s.dth_lo, d.ldw, (long long)M * d.ldw,
+                               M, d.tl, d.B, s.amax + 2, stream))
+            return rc;
+    } else if (int rc = split_tf32(dtheta_w, d.ldw, (long long)M * d.ldw, s.dth_hi, s.dth_lo, d.ldw,
+                                   (long long)M * d.ldw, M, d.tl, d.B, stream)) {
         return rc;
+    }
+    const unsigned* ax = s.half ? s.amax + 0 : nullptr;
+    const unsigned* au = s.half ? s.amax + 1 : nullptr;
+    const unsigned* ad = s.half ? s.amax + 2 : nullptr;
     {
         // dx (M x D) (+)= sum_b dtheta_b (M x tl, K-major) * u_b^T (u_b: D rows x tl, K-major)
-        const SplitOperand A = {s.dth_hi, s.dth_lo, 0, d.ldw, (long long)M * d.ldw};
-        const SplitOperand Bop = {s.u_hi, s.u_lo, 0, d.ldw, (long long)d.D * d.ldw};
+        const SplitOperand A = {s.dth_hi, s.dth_lo, 0, d.ldw, (long long)M * d.ldw, ad};
+        const SplitOperand Bop = {s.u_hi, s.u_lo, 0, d.ldw, (long long)d.D * d.ldw, au};
         const GemmShape shape = {M, d.D, d.tl, d.B, 1, overwrite_dx ? 0 : 1, d.D, 0};
         if (int rc = gemm_tf32x3(A, Bop, dx, shape, stream)) return rc;
     }
     {
         // du_b (D x tl) += x^T (x stored M rows x D: K rows, output-row index contiguous -> MN-major)
         //                  * dtheta_b (M x tl: K rows, N contiguous -> MN-major)
-        const SplitOperand A = {s.x_hi, s.x_lo, 1, d.D, 0};
-        const SplitOperand Bop = {s.dth_hi, s.dth_lo, 1, d.ldw, (long long)M * d.ldw};
+        const SplitOperand A = {s.x_hi, s.x_lo, 1, d.D, 0, ax};
+        const SplitOperand Bop = {s.dth_hi, s.dth_lo, 1, d.ldw, (long long)M * d.ldw, ad};
         const GemmShape shape = {d.D, d.tl, M, d.B, 0, 1, d.L, (long long)d.D * d.L};
         return gemm_tf32x3(A, Bop, du + d.t0, shape, stream);
     }

@@ -23,7 +23,8 @@ struct ProjDims {
     int tl;
 };
 
-// Scratch for the TF32 hi/lo parts of the operands (caller-owned, inside the operator workspace).
+// Scratch for the hi/lo parts of the operands (caller-owned, inside the operator workspace); sized for TF32
+// parts (one float per value and part), FP16 parts use half of it.
 struct ProjScratch {
     float* x_hi;      // (D*N, D)
     float* x_lo;
@@ -31,7 +32,9 @@ struct ProjScratch {
     float* u_lo;
     float* dth_hi;    // (B, D*N, ldw)    window of dtheta
     float* dth_lo;
+    unsigned* amax;   // FP16 parts: bit patterns of max|x|, max|u window|, max|dtheta window|
     int use_tensor_cores;   // decided once per operator call by proj_begin()
+    int half;               // 1: FP16 parts (the buffers above hold halves), 0: TF32 parts
 };
 
 // floats needed behind ProjScratch for a window pitch ldw
@@ -52,6 +55,7 @@ int proj_adjoints(const ProjDims& d, const float* dtheta_w, const float* x, cons
                   bool overwrite_dx, ProjScratch& s, cudaStream_t stream);
 
 void set_error(const char* fmt, ...);
-void set_gemm_backend(int mode);   // 0: tensor cores when the shapes allow, 1: always the library SGEMM
+void set_gemm_backend(int mode);   // 0: tensor cores, FP16 parts when the pitches allow; 1: library SGEMM; 2: TF32 parts
+int gemm_backend();
 
 }  // namespace aussm

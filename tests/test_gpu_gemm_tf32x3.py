@@ -1,4 +1,5 @@
-"""The tcgen05 three-term TF32 GEMM against a float64 product (through the C ABI)."""
+"""The tcgen05 three-term split GEMM (FP16 parts by default, TF32 parts as option or when a pitch is not a
+multiple of 8) against a float64 product (through the C ABI)."""
 import pytest
 import torch
 
@@ -38,9 +39,17 @@ CASES = [
 ]
 
 
+@pytest.fixture(params=["f16", "tf32"])
+def parts(request):
+    """gemm_backend 0: FP16 parts where every pitch is a multiple of 8; 2: TF32 parts always"""
+    _lib.set_option("gemm_backend", 0 if request.param == "f16" else 2)
+    yield request.param
+    _lib.set_option("gemm_backend", 0)
+
+
 @pytest.mark.parametrize("majors", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("case", CASES)
-def test_gemm_matches_float64(case, majors):
+def test_gemm_matches_float64(case, majors, parts):
     M, N, K, batches, a_b, b_b, reduce = case
     a_mn, b_mn = majors
     if (a_mn and M % 4) or (b_mn and N % 4) or K % 4:
@@ -62,7 +71,7 @@ def test_gemm_matches_float64(case, majors):
         assert err <= 3e-6 * scale, f"beta={beta}: max error {err:.3e} on scale {scale:.3e}"
 
 
-def test_large_k_accuracy_is_float32_like():
+def test_large_k_accuracy_is_float32_like(parts):
     M, N, K = 256, 256, 4096
     gen = torch.Generator().manual_seed(1)
     A = torch.randn(M, K, generator=gen)
@@ -72,5 +81,28 @@ def test_large_k_accuracy_is_float32_like():
     want = A.double() @ B.double().T
     err_tc = (C.cpu().double() - want).abs().max().item()
     err_fp32 = ((A.cuda() @ B.cuda().T).cpu().double() - want).abs().max().item()
-    print(f"K=4096: tf32x3 max error {err_tc:.3e}, float32 matmul {err_fp32:.3e}")
+    print(f"K=4096: {parts} parts max error {err_tc:.3e}, float32 matmul {err_fp32:.3e}")
     assert err_tc <= 4 * err_fp32 + 1e-4
+
+
+@pytest.mark.parametrize("scales", [(1e-20, 1e15), (3e7, 2e-9), (1.0, 1.0)])
+def test_f16_parts_keep_accuracy_over_the_float32_range(scales):
+    """The FP16 parts are taken after a power-of-two scaling by the tensor's largest magnitude, so tensors far
+    outside FP16's own range, and entries 1e6 times smaller than the largest one, keep float32-like accuracy."""
+    M, N, K = 128, 256, 512
+    gen = torch.Generator().manual_seed(5)
+    A = torch.randn(M, K, generator=gen) * scales[0]
+    B = torch.randn(N, K, generator=gen) * scales[1]
+    A[::3] *= 1e-6                                # rows far below the tensor's maximum
+    B[:, ::5] *= 1e-4
+    C = torch.empty(M, N, device="cuda")
+    _lib.set_option("gemm_backend", 0)
+    _gemm(A.cuda(), 0, 0, B.cuda(), 0, 0, C, M, N, K, 1, 0, 0)
+    want = A.double() @ B.double().T
+    got = C.cpu().double()
+    # row-wise scale: every output row is judged against its own magnitude
+    row_scale = (A.double().abs() @ B.double().abs().T).clamp_min(1e-300)
+    rel = ((got - want).abs() / row_scale).max().item()
+    ref = (((A.cuda() @ B.cuda().T).cpu().double() - want).abs() / row_scale).max().item()
+    print(f"scales {scales}: f16 parts {rel:.3e}, float32 matmul {ref:.3e} (relative to sum |a||b|)")
+    assert rel <= 5e-7
