@@ -3,7 +3,9 @@
 // loops of csrc/cuda/ssm_adaptive_unitary_forward.cu:83-110 and the atomics of
 // ssm_adaptive_unitary_backward.cu:419-490 of the reference).
 //
-// One CTA computes a 128 x 128 tile of C.  Roles: warp 0 = TMA producer (one
+// One CTA computes a 128 x 256 tile of C (the operand stream from L2 bounds this kernel: 64 KB per 128 x 128
+// K block kept every SM at its ~60 GB/s share of the L2 bandwidth, so the tile is as wide as tensor memory
+// allows).  Roles: warp 0 = TMA producer (one
 // lane), warp 1 = MMA issuer (one lane; the warp also owns the TMEM
 // allocation), warps 2-9 = accumulate/epilogue (TMEM -> registers -> global).
 // Operands arrive pre-split into TF32 hi/lo parts; per 32-deep K block the
@@ -36,23 +38,25 @@
 namespace aussm {
 namespace {
 
-constexpr int BM = 128, BN = 128;
+constexpr int BM = 128, BN = 256;
 constexpr int BK_BYTES = 128;                        // one K block = one 128-byte swizzle row: 32 TF32 or 64 FP16 values
-constexpr int STAGES = 3;
+constexpr int STAGES = 2;
 constexpr int A_TILE_BYTES = BM * BK_BYTES;          // 16 KB
-constexpr int B_TILE_BYTES = BN * BK_BYTES;          // 16 KB
-constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // hi + lo of both operands: 64 KB
+constexpr int B_TILE_BYTES = BN * BK_BYTES;          // 32 KB
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // hi + lo of both operands: 96 KB
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + slack for 1024-byte alignment
 // Tensor-memory accumulation truncates instead of rounding, so a long K loop drifts (measured 3.5e-5 relative
-// at K = 4096).  The K loop is therefore cut into chunks of CHUNK_KB blocks: each chunk accumulates from zero
-// into one of two TMEM buffers and the epilogue warps add the finished chunk into float32 registers
-// (round-to-nearest) while the next chunk runs.  Each buffer holds two accumulators: the hi*hi products and the
-// two small cross terms, so that adding the tiny terms does not cost the big sum an extra truncation.
+// at K = 4096).  The K loop is therefore cut into chunks of 64 K values: each chunk accumulates from zero in
+// tensor memory and the epilogue warps add the finished chunk into float32 registers (round-to-nearest).  The
+// hi*hi products and the two small cross terms go to separate accumulators (adding the tiny terms must not
+// cost the big sum extra truncations).  The 512 columns hold such a pair for each 128-column half of the tile,
+// and the halves take turns: while the tensor core works on one half of a chunk, the epilogue warps drain the
+// other.
 // FP16 parts: the scaled low part is stored times 2^LO_SHIFT (see split_f16_kernel)
 constexpr int LO_SHIFT = 11;
-constexpr int ACC_COLS = 2 * BN;                     // main + cross accumulator of one buffer
-constexpr int TMEM_COLS = 2 * ACC_COLS;              // 512: two buffers
-constexpr int EPI_WARPS = 8;                         // two per TMEM lane quarter, 64 columns each
+constexpr int MMA_N = 128;                           // the tile's two column halves take turns (see below)
+constexpr int TMEM_COLS = 2 * BN;                    // 512: per column half a main and a cross accumulator
+constexpr int EPI_WARPS = 8;                         // two per TMEM lane quarter, 64 columns of each half
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
 
 struct GemmKernelParams {
@@ -132,21 +136,26 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                  : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
+// two 16-column loads of this warp's 32 lanes in flight, one wait
+__device__ __forceinline__ void tmem_ld16_pair(uint32_t ta, uint32_t tb, float (&va)[16], float (&vb)[16]) {
+    uint32_t r[16], q[16];
+#define AUSSM_LD16(R, T)                                                                                          \
+    asm volatile(                                                                                                 \
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "                                                                 \
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"                          \
+        : "=r"(R[0]), "=r"(R[1]), "=r"(R[2]), "=r"(R[3]), "=r"(R[4]), "=r"(R[5]), "=r"(R[6]), "=r"(R[7]),        \
+          "=r"(R[8]), "=r"(R[9]), "=r"(R[10]), "=r"(R[11]), "=r"(R[12]), "=r"(R[13]), "=r"(R[14]), "=r"(R[15])   \
+        : "r"(T)                                                                                                  \
+        : "memory")
+    AUSSM_LD16(r, ta);
+    AUSSM_LD16(q, tb);
+#undef AUSSM_LD16
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 16; ++i) {
+        va[i] = __uint_as_float(r[i]);
+        vb[i] = __uint_as_float(q[i]);
+    }
 }
 
 // Shared-memory matrix descriptors (64 bit): start address >> 4 in bits 0-13,
@@ -182,7 +191,7 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t tile_saddr, int kk) {
 template <int A_MN, int B_MN, bool HALF>
 __device__ __forceinline__ constexpr uint32_t instr_desc() {
     return (1u << 4) | ((HALF ? 0u : 2u) << 7) | ((HALF ? 0u : 2u) << 10) | ((uint32_t)A_MN << 15) |
-           ((uint32_t)B_MN << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+           ((uint32_t)B_MN << 16) | ((uint32_t)(MMA_N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 template <int A_MN, int B_MN, bool HALF>
@@ -212,9 +221,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], EPI_WARPS);
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(&acc_full[h], 1);
+            mbar_init(&acc_empty[h], EPI_WARPS);
         }
         failed = 0;
         fence_mbar_init();
@@ -267,102 +276,108 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // ---- MMA issuer: one chunk of CHUNK_KB K-blocks per TMEM buffer ----
+            // ---- MMA issuer: per chunk of CHUNK_KB K-blocks, column half 0 then column half 1 ----
             constexpr uint32_t idesc = instr_desc<A_MN, B_MN, HALF>();
             bool ok = true;
-            int it = 0;
             for (int c = 0; c < nchunks && ok; ++c) {
-                const int buf = c & 1;
-                const uint32_t aph = (uint32_t)(c >> 1) & 1u;
-                if (!mbar_wait_bounded(&acc_empty[buf], aph ^ 1u, p.status)) { failed = 1; ok = false; break; }
-                tc_fence_after();
-                const uint32_t acc_main = tmem_base + (uint32_t)(buf * ACC_COLS);
-                const uint32_t acc_cross = acc_main + BN;
-                for (int j = 0; j < CHUNK_KB && it < total; ++j, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                    if (!mbar_wait_bounded(&full_bar[s], ph, p.status)) { failed = 1; ok = false; break; }
+                const int it0 = c * CHUNK_KB, it1 = min(total, it0 + CHUNK_KB);
+                for (int h = 0; h < 2 && ok; ++h) {
+                    // the epilogue warps have taken this half of chunk c-1 out of tensor memory
+                    if (!mbar_wait_bounded(&acc_empty[h], ((uint32_t)c & 1u) ^ 1u, p.status)) { failed = 1; ok = false; break; }
                     tc_fence_after();
-                    const uint32_t st = smem_addr(smem + s * STAGE_BYTES);
-                    const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES, b_hi = st + 2 * A_TILE_BYTES,
-                                   b_lo = st + 2 * A_TILE_BYTES + B_TILE_BYTES;
-#pragma unroll
-                    for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
-                        const uint64_t ah = operand_desc<A_MN, HALF>(a_hi, kk), al = operand_desc<A_MN, HALF>(a_lo, kk);
-                        const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk), bl = operand_desc<B_MN, HALF>(b_lo, kk);
-                        const uint32_t first = (j > 0 || kk > 0) ? 1u : 0u;
-                        if (HALF) {
-                            umma_f16(acc_main, ah, bh, idesc, first);
-                            umma_f16(acc_cross, ah, bl, idesc, first);
-                            umma_f16(acc_cross, al, bh, idesc, 1u);
-                        } else {
-                            umma_tf32(acc_main, ah, bh, idesc, first);
-                            umma_tf32(acc_cross, ah, bl, idesc, first);
-                            umma_tf32(acc_cross, al, bh, idesc, 1u);
+                    const uint32_t acc_main = tmem_base + (uint32_t)(h * 2 * MMA_N), acc_cross = acc_main + MMA_N;
+                    for (int it = it0; it < it1; ++it) {
+                        const int s = it % STAGES;
+                        if (h == 0) {
+                            const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                            if (!mbar_wait_bounded(&full_bar[s], ph, p.status)) { failed = 1; ok = false; break; }
+                            tc_fence_after();
                         }
+                        const uint32_t st = smem_addr(smem + s * STAGE_BYTES);
+                        const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES;
+                        // rows [128 h, 128 h + 128) of the B parts: 16 KB further in either layout
+                        const uint32_t b_hi = st + 2 * A_TILE_BYTES + h * (MMA_N * BK_BYTES),
+                                       b_lo = b_hi + B_TILE_BYTES;
+#pragma unroll
+                        for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
+                            const uint64_t ah = operand_desc<A_MN, HALF>(a_hi, kk), al = operand_desc<A_MN, HALF>(a_lo, kk);
+                            const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk), bl = operand_desc<B_MN, HALF>(b_lo, kk);
+                            const uint32_t first = (it > it0 || kk > 0) ? 1u : 0u;
+                            if (HALF) {
+                                umma_f16(acc_main, ah, bh, idesc, first);
+                                umma_f16(acc_cross, ah, bl, idesc, first);
+                                umma_f16(acc_cross, al, bh, idesc, 1u);
+                            } else {
+                                umma_tf32(acc_main, ah, bh, idesc, first);
+                                umma_tf32(acc_cross, ah, bl, idesc, first);
+                                umma_tf32(acc_cross, al, bh, idesc, 1u);
+                            }
+                        }
+                        if (h == 1) umma_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
                     }
-                    umma_commit(&empty_bar[s]);      // frees the stage when these MMAs have read it
+                    umma_commit(&acc_full[h]);           // half complete (arrives even after a failed wait)
                 }
-                umma_commit(&acc_full[buf]);         // chunk complete (arrives even after a failed wait)
             }
         }
     } else {
-        // ---- accumulate + epilogue: warps 2..9; TMEM lane quarter = warp % 4, column half = (warp - 2) / 4 ----
+        // ---- accumulate + epilogue: warps 2..9; TMEM lane quarter = warp % 4, 64-column slice = (warp - 2) / 4 ----
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
-        float acc[64];
+        const int slice = (warp - 2) >> 2;
+        float acc[2][64];                        // scaled units (FP16 parts): the scales come off once, at the end
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.f;
-        // FP16 parts carry power-of-two scales: undo them (exactly) when a chunk is added
-        float unscale_a = 1.f, unscale_b = 1.f, cross_scale = 1.f;
-        if (HALF) {
-            unscale_a = pow2f(-scale_exponent(*p.amax_a));
-            unscale_b = pow2f(-scale_exponent(*p.amax_b));
-            cross_scale = pow2f(-LO_SHIFT);
-        }
+        for (int i = 0; i < 64; ++i) acc[0][i] = acc[1][i] = 0.f;
+        const float cross_scale = HALF ? pow2f(-LO_SHIFT) : 1.f;
         bool ok = true;
         for (int c = 0; c < nchunks && ok; ++c) {
-            const int buf = c & 1;
-            const uint32_t aph = (uint32_t)(c >> 1) & 1u;
-            ok = mbar_wait_bounded(&acc_full[buf], aph, p.status);
-            tc_fence_after();
-            if (ok) {
-                const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * ACC_COLS + half * 64);
 #pragma unroll
-                for (int part = 0; part < 2; ++part) {
-                    float vm[32], vc[32];
-                    tmem_ld32(t0 + part * 32, vm);            // hi*hi
-                    tmem_ld32(t0 + BN + part * 32, vc);       // hi*lo + lo*hi
+            for (int h = 0; h < 2; ++h) {
+                if (ok) ok = mbar_wait_bounded(&acc_full[h], (uint32_t)c & 1u, p.status);
+                tc_fence_after();
+                if (ok) {
+                    const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 2 * MMA_N + slice * 64);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (HALF) acc[part * 32 + i] += (fmaf(vc[i], cross_scale, vm[i]) * unscale_a) * unscale_b;
-                        else acc[part * 32 + i] += vm[i] + vc[i];
+                    for (int part = 0; part < 4; ++part) {
+                        float vm[16], vc[16];
+                        tmem_ld16_pair(t0 + part * 16, t0 + MMA_N + part * 16, vm, vc);   // hi*hi ; hi*lo + lo*hi
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            acc[h][part * 16 + i] = fmaf(vc[i], cross_scale, acc[h][part * 16 + i] + vm[i]);
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[h]);        // the issuer may overwrite this half
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);      // the issuer may overwrite this buffer
         }
         if (ok && !failed) {
             const int row = m0 + quarter * 32 + lane;
+            float ua = 1.f, ub = 1.f;
+            if (HALF) {                        // exact power-of-two scales, applied one after the other
+                ua = pow2f(-scale_exponent(*p.amax_a));
+                ub = pow2f(-scale_exponent(*p.amax_b));
+            }
             if (row < p.M) {
-                const int col0 = n0 + half * 64;
-                float* crow = p.C + (long long)zb * p.c_batch_stride + (long long)row * p.ldc + col0;
 #pragma unroll
-                for (int g = 0; g < 16; ++g) {
-                    const int col = col0 + 4 * g;
-                    float* dst = crow + 4 * g;
-                    if (col + 3 < p.N) {
-                        float4 o = make_float4(acc[4 * g], acc[4 * g + 1], acc[4 * g + 2], acc[4 * g + 3]);
-                        if (p.beta) {
-                            const float4 cin = *reinterpret_cast<const float4*>(dst);
-                            o.x += cin.x; o.y += cin.y; o.z += cin.z; o.w += cin.w;
+                for (int h = 0; h < 2; ++h) {
+                    const int col0 = n0 + h * MMA_N + slice * 64;
+                    float* crow = p.C + (long long)zb * p.c_batch_stride + (long long)row * p.ldc + col0;
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) {
+                        const int col = col0 + 4 * g;
+                        float* dst = crow + 4 * g;
+                        float4 o = make_float4((acc[h][4 * g] * ua) * ub, (acc[h][4 * g + 1] * ua) * ub,
+                                               (acc[h][4 * g + 2] * ua) * ub, (acc[h][4 * g + 3] * ua) * ub);
+                        if (col + 3 < p.N) {
+                            if (p.beta) {
+                                const float4 cin = *reinterpret_cast<const float4*>(dst);
+                                o.x += cin.x; o.y += cin.y; o.z += cin.z; o.w += cin.w;
+                            }
+                            *reinterpret_cast<float4*>(dst) = o;
+                        } else {
+                            const float ov[4] = {o.x, o.y, o.z, o.w};
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < p.N) dst[e] = ov[e] + (p.beta ? dst[e] : 0.f);
                         }
-                        *reinterpret_cast<float4*>(dst) = o;
-                    } else {
-                        for (int e = 0; e < 4; ++e)
-                            if (col + e < p.N) dst[e] = acc[4 * g + e] + (p.beta ? dst[e] : 0.f);
                     }
                 }
             }
