@@ -1,6 +1,7 @@
 """Timing sweep of the scan operators (CUDA events, scan cores with inputs resident in HBM).
 
     python -m aussm_b200.sweep [--config 1|2] [--steps K]
+    python -m aussm_b200.sweep --gemm M N K [--steps K]      (the split GEMM alone, theta-like operand layouts)
 
 config 1: unitary scan core, batch 16, d_inner 1024, d_state 16, seq in {256, 1024, 4096, 16384}
 config 2: real (Mamba S6), complex and unitary scan cores at batch 8, d_inner 2048, d_state 16, seq 4096
@@ -78,12 +79,36 @@ def _case(kind, b, d, n, l, steps):
                       "note": "through the autograd wrappers (output allocation included)"}), flush=True)
 
 
+def _gemm_case(M, N, K, steps):
+    """C (M x N) = A (M x K, K contiguous) * B (K x N, N contiguous) through aussm_b200_gemm_tf32x3."""
+    from aussm_b200 import _lib
+    lib = _lib.load()
+    A = torch.randn(M, K, device="cuda")
+    B = torch.randn(K, N, device="cuda")
+    C = torch.empty(M, N, device="cuda")
+    ws = torch.empty(lib.aussm_b200_gemm_tf32x3_workspace_bytes(M, N, K, 1, 0, 0), dtype=torch.uint8, device="cuda")
+
+    def call():
+        _lib.check(lib.aussm_b200_gemm_tf32x3(A.data_ptr(), 0, 0, B.data_ptr(), 1, 0, C.data_ptr(), M, N, K, 1, 0, 0,
+                                              ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream),
+                   "gemm_tf32x3")
+
+    ms = _time(call, steps, warmup=3)
+    print(json.dumps({"kind": "split gemm", "M": M, "N": N, "K": K, "ms": ms,
+                      "tflops_float32_equivalent": 2.0 * M * N * K / ms / 1e9,
+                      "device_status": aussm_b200.device_status(),
+                      "note": "includes the two hi/lo split passes of the operands"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--gemm", type=int, nargs=3, metavar=("M", "N", "K"))
     a = ap.parse_args()
-    if a.config == 1:
+    if a.gemm:
+        _gemm_case(*a.gemm, a.steps)
+    elif a.config == 1:
         for l in (256, 1024, 4096, 16384):
             _case("unitary", 16, 1024, 16, l, a.steps)
     else:
