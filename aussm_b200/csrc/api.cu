@@ -180,6 +180,8 @@ int aussm_b200_set_option(const char* name, int value) {
     else if (!strcmp(name, "blocks_per_sm")) o.blocks_per_sm = value;
     else if (!strcmp(name, "gemm_tile")) g_window_override = value;
     else if (!strcmp(name, "gemm_backend")) set_gemm_backend(value);
+    else if (!strcmp(name, "gemm_pair")) set_gemm_pair(value);
+    else if (!strcmp(name, "gemm_probe")) set_gemm_probe(value);
     else {
         set_error("unknown option '%s'", name);
         return AUSSM_EINVAL;

@@ -29,6 +29,7 @@
 #include <stdint.h>
 
 #include <mutex>
+#include <type_traits>
 
 #include "../../include/aussm_b200.h"
 #include "common.cuh"
@@ -71,6 +72,7 @@ struct GemmKernelParams {
     int* status;
     const unsigned* amax_a;   // FP16 parts: bit patterns of max|a|, max|b| (the parts are scaled by a power of two)
     const unsigned* amax_b;
+    int probe;                // measurement only (results invalid): 1 no accumulator drain, 2 no refills, 4 no MMAs
 };
 
 // Power-of-two scale that brings a tensor whose largest magnitude has the bit pattern `maxbits` to about 2^14
@@ -186,6 +188,16 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t tile_saddr, int kk) {
     return smem_desc(tile_saddr + kk * 32, 16, 1024, 2);
 }
 
+// Accumulation chunks.  A chunk is KC consecutive K blocks accumulated in tensor memory before the epilogue warps
+// add it to their float32 registers; the chunks of the tile's two column halves are offset by KC/2 blocks, so the
+// halves never finish a chunk at the same K block: the half that starts a new chunk is issued second and its
+// drain hides behind the other half's MMAs.
+__device__ __forceinline__ bool half_starts(int h, int it, int kc) { return it == 0 || (it % kc) == (h ? kc / 2 : 0); }
+__device__ __forceinline__ bool half_ends(int h, int it, int total, int kc) {
+    return it == total - 1 || half_starts(h, it + 1, kc);
+}
+__device__ __forceinline__ int first_half(int it, int kc) { return (it > 0 && half_starts(0, it, kc)) ? 1 : 0; }
+
 // Instruction descriptor, float32 accumulate: c_format=1 (bits 4-5), a/b format (bits 7-9, 10-12: TF32=2 for
 // kind::tf32, F16=0 for kind::f16), a/b major (bits 15, 16), N>>3 (bits 17-22), M>>4 (bits 24-28).
 template <int A_MN, int B_MN, bool HALF>
@@ -211,8 +223,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     constexpr int BK = HALF ? 64 : 32;                         // K values per block
     constexpr int MNBOX = HALF ? 64 : 32;                      // row elements per MN-major TMA box
     constexpr int MNBOX_BYTES = MNBOX * BK_BYTES;
-    constexpr int CHUNK_KB = HALF ? 1 : 2;                     // 64 K values per chunk either way
+    constexpr int CHUNK_KB = HALF ? 4 : 4;                     // K values per chunk: 256 (FP16 parts) / 128 (TF32 parts)
     const int kblocks = (p.K + BK - 1) / BK;
+    constexpr int PROBE_STAGES = STAGES;
+    const bool PROBE_LEADER = true;
     const int total = kblocks * p.kbatches;
     const int nchunks = (total + CHUNK_KB - 1) / CHUNK_KB;
 
@@ -242,6 +256,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, p.status)) { failed = 1; break; }
+                if ((p.probe & 2) && it >= PROBE_STAGES) {       // stale operands: no traffic from L2
+                    if (PROBE_LEADER) mbar_arrive(&full_bar[s]);
+                    continue;
+                }
                 const int kb = it % kblocks;
                 const int batch = p.kbatches > 1 ? it / kblocks : zb;
                 const int ba = p.a_batched ? batch : 0, bb = p.b_batched ? batch : 0;
@@ -279,44 +297,40 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
             // ---- MMA issuer: per chunk of CHUNK_KB K-blocks, column half 0 then column half 1 ----
             constexpr uint32_t idesc = instr_desc<A_MN, B_MN, HALF>();
             bool ok = true;
-            for (int c = 0; c < nchunks && ok; ++c) {
-                const int it0 = c * CHUNK_KB, it1 = min(total, it0 + CHUNK_KB);
-                for (int h = 0; h < 2 && ok; ++h) {
-                    // the epilogue warps have taken this half of chunk c-1 out of tensor memory
-                    if (!mbar_wait_bounded(&acc_empty[h], ((uint32_t)c & 1u) ^ 1u, p.status)) { failed = 1; ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t acc_main = tmem_base + (uint32_t)(h * 2 * MMA_N), acc_cross = acc_main + MMA_N;
-                    for (int it = it0; it < it1; ++it) {
-                        const int s = it % STAGES;
-                        if (h == 0) {
-                            const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                            if (!mbar_wait_bounded(&full_bar[s], ph, p.status)) { failed = 1; ok = false; break; }
-                            tc_fence_after();
-                        }
-                        const uint32_t st = smem_addr(smem + s * STAGE_BYTES);
-                        const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES;
-                        // rows [128 h, 128 h + 128) of the B parts: 16 KB further in either layout
-                        const uint32_t b_hi = st + 2 * A_TILE_BYTES + h * (MMA_N * BK_BYTES),
-                                       b_lo = b_hi + B_TILE_BYTES;
-#pragma unroll
-                        for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
-                            const uint64_t ah = operand_desc<A_MN, HALF>(a_hi, kk), al = operand_desc<A_MN, HALF>(a_lo, kk);
-                            const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk), bl = operand_desc<B_MN, HALF>(b_lo, kk);
-                            const uint32_t first = (it > it0 || kk > 0) ? 1u : 0u;
-                            if (HALF) {
-                                umma_f16(acc_main, ah, bh, idesc, first);
-                                umma_f16(acc_cross, ah, bl, idesc, first);
-                                umma_f16(acc_cross, al, bh, idesc, 1u);
-                            } else {
-                                umma_tf32(acc_main, ah, bh, idesc, first);
-                                umma_tf32(acc_cross, ah, bl, idesc, first);
-                                umma_tf32(acc_cross, al, bh, idesc, 1u);
-                            }
-                        }
-                        if (h == 1) umma_commit(&empty_bar[s]);   // frees the stage when these MMAs have read it
+            int ch[2] = {0, 0};                       // chunks finished per column half
+            for (int it = 0; it < total && ok; ++it) {
+                const int s = it % STAGES;
+                if (!mbar_wait_bounded(&full_bar[s], (uint32_t)(it / STAGES) & 1u, p.status)) { failed = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t st = smem_addr(smem + s * STAGE_BYTES);
+                const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES;
+                const int first = first_half(it, CHUNK_KB);
+                for (int q = 0; q < 2 && ok; ++q) {
+                    const int h = q == 0 ? first : 1 - first;
+                    const bool starts = half_starts(h, it, CHUNK_KB);
+                    if (starts) {
+                        // the epilogue warps have taken this half's previous chunk out of tensor memory
+                        if (!mbar_wait_bounded(&acc_empty[h], ((uint32_t)ch[h] & 1u) ^ 1u, p.status)) { failed = 1; ok = false; break; }
+                        tc_fence_after();
                     }
-                    umma_commit(&acc_full[h]);           // half complete (arrives even after a failed wait)
+                    const uint32_t acc_main = tmem_base + (uint32_t)(h * 2 * MMA_N), acc_cross = acc_main + MMA_N;
+                    const uint32_t b_hi = st + 2 * A_TILE_BYTES + h * (MMA_N * BK_BYTES), b_lo = b_hi + B_TILE_BYTES;
+                    if (!(p.probe & 4))
+#pragma unroll
+                    for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
+                        const uint64_t ah = operand_desc<A_MN, HALF>(a_hi, kk), al = operand_desc<A_MN, HALF>(a_lo, kk);
+                        const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk), bl = operand_desc<B_MN, HALF>(b_lo, kk);
+                        const uint32_t acc_flag = (starts && kk == 0) ? 0u : 1u;
+                        if (HALF) umma_f16(acc_main, ah, bh, idesc, acc_flag); else umma_tf32(acc_main, ah, bh, idesc, acc_flag);
+                        if (HALF) umma_f16(acc_cross, ah, bl, idesc, acc_flag); else umma_tf32(acc_cross, ah, bl, idesc, acc_flag);
+                        if (HALF) umma_f16(acc_cross, al, bh, idesc, 1u); else umma_tf32(acc_cross, al, bh, idesc, 1u);
+                    }
+                    if (half_ends(h, it, total, CHUNK_KB)) {
+                        umma_commit(&acc_full[h]);          // chunk of this half complete
+                        ++ch[h];
+                    }
                 }
+                umma_commit(&empty_bar[s]);                 // frees the stage when these MMAs have read it
             }
         }
     } else {
@@ -328,25 +342,35 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
         for (int i = 0; i < 64; ++i) acc[0][i] = acc[1][i] = 0.f;
         const float cross_scale = HALF ? pow2f(-LO_SHIFT) : 1.f;
         bool ok = true;
-        for (int c = 0; c < nchunks && ok; ++c) {
+        int ch0 = 0, ch1 = 0;                            // chunks drained per column half
+        auto drain = [&](auto H, int& chn) {
+            constexpr int h = decltype(H)::value;
+            if (ok) ok = mbar_wait_bounded(&acc_full[h], (uint32_t)chn & 1u, p.status);
+            tc_fence_after();
+            if (ok && !(p.probe & 1)) {
+                const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 2 * MMA_N + slice * 64);
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (ok) ok = mbar_wait_bounded(&acc_full[h], (uint32_t)c & 1u, p.status);
-                tc_fence_after();
-                if (ok) {
-                    const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 2 * MMA_N + slice * 64);
+                for (int part = 0; part < 4; ++part) {
+                    float vm[16], vc[16];
+                    tmem_ld16_pair(t0 + part * 16, t0 + MMA_N + part * 16, vm, vc);   // hi*hi ; hi*lo + lo*hi
 #pragma unroll
-                    for (int part = 0; part < 4; ++part) {
-                        float vm[16], vc[16];
-                        tmem_ld16_pair(t0 + part * 16, t0 + MMA_N + part * 16, vm, vc);   // hi*hi ; hi*lo + lo*hi
-#pragma unroll
-                        for (int i = 0; i < 16; ++i)
-                            acc[h][part * 16 + i] = fmaf(vc[i], cross_scale, acc[h][part * 16 + i] + vm[i]);
-                    }
+                    for (int i = 0; i < 16; ++i)
+                        acc[h][part * 16 + i] = fmaf(vc[i], cross_scale, acc[h][part * 16 + i] + vm[i]);
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[h]);        // the issuer may overwrite this half
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[h]);            // the issuer may start this half's next chunk
+            ++chn;
+        };
+        for (int it = 0; it < total; ++it) {
+            const int first = first_half(it, CHUNK_KB);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int h = q == 0 ? first : 1 - first;
+                if (!half_ends(h, it, total, CHUNK_KB)) continue;
+                if (h == 0) drain(std::integral_constant<int, 0>{}, ch0);
+                else drain(std::integral_constant<int, 1>{}, ch1);
             }
         }
         if (ok && !failed) {
@@ -386,6 +410,300 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Two-CTA version: a cluster of two CTAs (the two SMs of a TPC) computes a 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  CTA r of the pair owns rows [128 r, 128 r + 128) of the tile (its A tile and its
+// accumulators) and supplies 64 of the 128 B rows of each column half, so each CTA draws 64 KB per K block from L2
+// for twice the arithmetic of a 128 x 128 tile (the operand stream is what bounds this GEMM).  The leader CTA
+// (rank 0) issues every MMA; copies of both CTAs complete on the leader's "full" barriers; tcgen05.commit
+// multicasts the "stage free" and "accumulator full" arrivals to both CTAs; the epilogue warps of both CTAs arrive
+// on the leader's "accumulator empty" barriers.  Every wait is bounded, and both CTAs always reach the final
+// cluster barrier.
+// ---------------------------------------------------------------------------
+constexpr int P_STAGES = 3;
+constexpr int P_B_HALF_BYTES = 64 * BK_BYTES;                   // this CTA's 64 rows of one column half: 8 KB
+constexpr int P_B_TILE_BYTES = 2 * P_B_HALF_BYTES;              // both halves of one part: 16 KB
+constexpr int P_STAGE_BYTES = 2 * A_TILE_BYTES + 2 * P_B_TILE_BYTES;   // 64 KB
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// copy of one box into this CTA's shared memory; the bytes are counted on the LEADER CTA's barrier (the address with
+// the CTA-rank bit of the pair cleared)
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                                 int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_addr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar) & 0xFEFFFFFFu), "r"(c0),
+        "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_holder, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(smem_holder)),
+                 "r"(ncols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+template <bool HALF>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    if (HALF) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+// arrives on the barrier at this offset in BOTH CTAs when all MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_addr(bar)), "h"((uint16_t)3)
+        : "memory");
+}
+// arrive on the barrier at this offset in the leader CTA (rank 0 of the pair)
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(smem_addr(bar)), "r"(0)
+        : "memory");
+}
+
+template <int A_MN, int B_MN, bool HALF>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_split3_pair_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
+                        const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
+                        const GemmKernelParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[P_STAGES], empty_bar[P_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_holder;
+    __shared__ int failed;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = (int)cluster_ctarank();                   // 0: leader
+    const int m0 = (blockIdx.x >> 1) * 256 + rank * BM, n0 = blockIdx.y * BN;
+    const int zb = blockIdx.z;
+    constexpr int BK = HALF ? 64 : 32;
+    constexpr int MNBOX = HALF ? 64 : 32;
+    constexpr int MNBOX_BYTES = MNBOX * BK_BYTES;
+    constexpr int CHUNK_KB = HALF ? 4 : 4;
+    const int kblocks = (p.K + BK - 1) / BK;
+    constexpr int PROBE_STAGES = P_STAGES;
+    const bool PROBE_LEADER = rank == 0;
+    const int total = kblocks * p.kbatches;
+    const int nchunks = (total + CHUNK_KB - 1) / CHUNK_KB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);          // used in the leader only: its producer's arrive + both CTAs' bytes
+            mbar_init(&empty_bar[s], 1);         // one multicast commit per use
+        }
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(&acc_full[h], 1);
+            mbar_init(&acc_empty[h], 2 * EPI_WARPS);   // used in the leader only: epilogue warps of both CTAs
+        }
+        failed = 0;
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) tmem_alloc_pair(&tmem_holder, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                  // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_holder;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer (both CTAs): own A rows, own 64 B rows of each column half ----
+            for (int it = 0; it < total; ++it) {
+                const int s = it % P_STAGES;
+                const uint32_t ph = (uint32_t)(it / P_STAGES) & 1u;
+                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, p.status)) { failed = 1; break; }
+                if ((p.probe & 2) && it >= PROBE_STAGES) {       // stale operands: no traffic from L2
+                    if (PROBE_LEADER) mbar_arrive(&full_bar[s]);
+                    continue;
+                }
+                const int kb = it % kblocks;
+                const int batch = p.kbatches > 1 ? it / kblocks : zb;
+                const int ba = p.a_batched ? batch : 0, bb = p.b_batched ? batch : 0;
+                uint8_t* st = smem + s * P_STAGE_BYTES;
+                uint8_t* a_hi = st;
+                uint8_t* a_lo = st + A_TILE_BYTES;
+                uint8_t* b_hi = st + 2 * A_TILE_BYTES;
+                uint8_t* b_lo = b_hi + P_B_TILE_BYTES;
+                if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * P_STAGE_BYTES);   // bytes of both CTAs
+                const int k0 = kb * BK;
+                if (A_MN) {
+#pragma unroll
+                    for (int i = 0; i < BM / MNBOX; ++i) {
+                        tma_load_3d_pair(a_hi + i * MNBOX_BYTES, &mapA_hi, &full_bar[s], m0 + MNBOX * i, k0, ba);
+                        tma_load_3d_pair(a_lo + i * MNBOX_BYTES, &mapA_lo, &full_bar[s], m0 + MNBOX * i, k0, ba);
+                    }
+                } else {
+                    tma_load_3d_pair(a_hi, &mapA_hi, &full_bar[s], k0, m0, ba);
+                    tma_load_3d_pair(a_lo, &mapA_lo, &full_bar[s], k0, m0, ba);
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int nb = n0 + h * MMA_N + rank * 64;       // this CTA's rows of column half h
+                    if (B_MN) {
+#pragma unroll
+                        for (int i = 0; i < 64 / MNBOX; ++i) {
+                            tma_load_3d_pair(b_hi + h * P_B_HALF_BYTES + i * MNBOX_BYTES, &mapB_hi, &full_bar[s],
+                                             nb + MNBOX * i, k0, bb);
+                            tma_load_3d_pair(b_lo + h * P_B_HALF_BYTES + i * MNBOX_BYTES, &mapB_lo, &full_bar[s],
+                                             nb + MNBOX * i, k0, bb);
+                        }
+                    } else {
+                        tma_load_3d_pair(b_hi + h * P_B_HALF_BYTES, &mapB_hi, &full_bar[s], k0, nb, bb);
+                        tma_load_3d_pair(b_lo + h * P_B_HALF_BYTES, &mapB_lo, &full_bar[s], k0, nb, bb);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // ---- MMA issuer (leader CTA only): per chunk, column half 0 then column half 1 ----
+            constexpr uint32_t idesc = (1u << 4) | ((HALF ? 0u : 2u) << 7) | ((HALF ? 0u : 2u) << 10) |
+                                       ((uint32_t)A_MN << 15) | ((uint32_t)B_MN << 16) |
+                                       ((uint32_t)(MMA_N >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            bool ok = true;
+            int ch[2] = {0, 0};                       // chunks finished per column half
+            for (int it = 0; it < total && ok; ++it) {
+                const int s = it % P_STAGES;
+                if (!mbar_wait_bounded(&full_bar[s], (uint32_t)(it / P_STAGES) & 1u, p.status)) { failed = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t st = smem_addr(smem + s * P_STAGE_BYTES);
+                const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES;
+                const int first = first_half(it, CHUNK_KB);
+                for (int q = 0; q < 2 && ok; ++q) {
+                    const int h = q == 0 ? first : 1 - first;
+                    const bool starts = half_starts(h, it, CHUNK_KB);
+                    if (starts) {
+                        // the epilogue warps have taken this half's previous chunk out of tensor memory
+                        if (!mbar_wait_bounded(&acc_empty[h], ((uint32_t)ch[h] & 1u) ^ 1u, p.status)) { failed = 1; ok = false; break; }
+                        tc_fence_after();
+                    }
+                    const uint32_t acc_main = tmem_base + (uint32_t)(h * 2 * MMA_N), acc_cross = acc_main + MMA_N;
+                    const uint32_t b_hi = st + 2 * A_TILE_BYTES + h * P_B_HALF_BYTES, b_lo = b_hi + P_B_TILE_BYTES;
+                    if (!(p.probe & 4))
+#pragma unroll
+                    for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
+                        const uint64_t ah = operand_desc<A_MN, HALF>(a_hi, kk), al = operand_desc<A_MN, HALF>(a_lo, kk);
+                        const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk), bl = operand_desc<B_MN, HALF>(b_lo, kk);
+                        const uint32_t acc_flag = (starts && kk == 0) ? 0u : 1u;
+                        umma_pair<HALF>(acc_main, ah, bh, idesc, acc_flag);
+                        umma_pair<HALF>(acc_cross, ah, bl, idesc, acc_flag);
+                        umma_pair<HALF>(acc_cross, al, bh, idesc, 1u);
+                    }
+                    if (half_ends(h, it, total, CHUNK_KB)) {
+                        umma_commit_pair(&acc_full[h]);          // chunk of this half complete
+                        ++ch[h];
+                    }
+                }
+                umma_commit_pair(&empty_bar[s]);                 // frees the stage when these MMAs have read it
+            }
+        }
+    } else {
+        // ---- accumulate + epilogue (both CTAs, own 128 rows) ----
+        const int quarter = warp & 3;
+        const int slice = (warp - 2) >> 2;
+        float acc[2][64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[0][i] = acc[1][i] = 0.f;
+        const float cross_scale = HALF ? pow2f(-LO_SHIFT) : 1.f;
+        bool ok = true;
+        int ch0 = 0, ch1 = 0;                            // chunks drained per column half
+        auto drain = [&](auto H, int& chn) {
+            constexpr int h = decltype(H)::value;
+            if (ok) ok = mbar_wait_bounded(&acc_full[h], (uint32_t)chn & 1u, p.status);
+            tc_fence_after();
+            if (ok && !(p.probe & 1)) {
+                const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 2 * MMA_N + slice * 64);
+#pragma unroll
+                for (int part = 0; part < 4; ++part) {
+                    float vm[16], vc[16];
+                    tmem_ld16_pair(t0 + part * 16, t0 + MMA_N + part * 16, vm, vc);   // hi*hi ; hi*lo + lo*hi
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        acc[h][part * 16 + i] = fmaf(vc[i], cross_scale, acc[h][part * 16 + i] + vm[i]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_leader(&acc_empty[h]);            // the issuer may start this half's next chunk
+            ++chn;
+        };
+        for (int it = 0; it < total; ++it) {
+            const int first = first_half(it, CHUNK_KB);
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int h = q == 0 ? first : 1 - first;
+                if (!half_ends(h, it, total, CHUNK_KB)) continue;
+                if (h == 0) drain(std::integral_constant<int, 0>{}, ch0);
+                else drain(std::integral_constant<int, 1>{}, ch1);
+            }
+        }
+        if (!ok) failed = 1;
+        if (ok && !failed) {
+            const int row = m0 + quarter * 32 + lane;
+            float ua = 1.f, ub = 1.f;
+            if (HALF) {
+                ua = pow2f(-scale_exponent(*p.amax_a));
+                ub = pow2f(-scale_exponent(*p.amax_b));
+            }
+            if (row < p.M) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int col0 = n0 + h * MMA_N + slice * 64;
+                    float* crow = p.C + (long long)zb * p.c_batch_stride + (long long)row * p.ldc + col0;
+#pragma unroll
+                    for (int g = 0; g < 16; ++g) {
+                        const int col = col0 + 4 * g;
+                        float* dst = crow + 4 * g;
+                        float4 o = make_float4((acc[h][4 * g] * ua) * ub, (acc[h][4 * g + 1] * ua) * ub,
+                                               (acc[h][4 * g + 2] * ua) * ub, (acc[h][4 * g + 3] * ua) * ub);
+                        if (col + 3 < p.N) {
+                            if (p.beta) {
+                                const float4 cin = *reinterpret_cast<const float4*>(dst);
+                                o.x += cin.x; o.y += cin.y; o.z += cin.z; o.w += cin.w;
+                            }
+                            *reinterpret_cast<float4*>(dst) = o;
+                        } else {
+                            const float ov[4] = {o.x, o.y, o.z, o.w};
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < p.N) dst[e] = ov[e] + (p.beta ? dst[e] : 0.f);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the leader's MMAs no longer read this CTA's shared memory; both may free and leave
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
 // ---- hi/lo split ----------------------------------------------------------
@@ -537,9 +855,32 @@ int launch(const CUtensorMap* maps, const GemmKernelParams& kp, dim3 grid, cudaS
     return AUSSM_OK;
 }
 
+template <int A_MN, int B_MN, bool HALF>
+int launch_pair(const CUtensorMap* maps, const GemmKernelParams& kp, dim3 grid, cudaStream_t stream) {
+    auto kern = gemm_split3_pair_kernel<A_MN, B_MN, HALF>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    if (e != cudaSuccess) {
+        set_error("gemm_tf32x3 (CTA pairs): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        return AUSSM_ECUDA;
+    }
+    kern<<<grid, NUM_THREADS, P_SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);   // cluster dims are static
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("gemm_tf32x3 (CTA pairs) launch: %s", cudaGetErrorString(e));
+        return AUSSM_ECUDA;
+    }
+    return AUSSM_OK;
+}
+
 bool ok16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+int g_gemm_pair = 0;     // option "gemm_pair": 1 = two-CTA kernel, 0 = one CTA per tile (default: measured equal or faster)
+int g_gemm_probe = 0;    // option "gemm_probe": knock-out switches for measurement (see GemmKernelParams)
+
 }  // namespace
+
+void set_gemm_pair(int on) { g_gemm_pair = on ? 1 : 0; }
+void set_gemm_probe(int bits) { g_gemm_probe = bits; }
 
 bool gemm_tf32x3_supported(const SplitOperand& A, const SplitOperand& B, const float* C, const GemmShape& s) {
     if (s.M <= 0 || s.N <= 0 || s.K <= 0 || s.batches <= 0) return false;
@@ -561,8 +902,10 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
     const bool half = A.amax != nullptr;
     if (int rc = make_map(&maps[0], A.hi, half, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
     if (int rc = make_map(&maps[1], A.lo, half, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
-    if (int rc = make_map(&maps[2], B.hi, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
-    if (int rc = make_map(&maps[3], B.lo, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, BN)) return rc;
+    const bool pair = g_gemm_pair != 0;
+    const int b_box_rows = pair ? 64 : BN;     // K-major B: a CTA of a pair copies 64 rows per column half
+    if (int rc = make_map(&maps[2], B.hi, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, b_box_rows)) return rc;
+    if (int rc = make_map(&maps[3], B.lo, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, b_box_rows)) return rc;
     GemmKernelParams kp;
     kp.C = C; kp.ldc = s.ldc; kp.c_batch_stride = s.c_batch_stride;
     kp.M = s.M; kp.N = s.N; kp.K = s.K;
@@ -572,12 +915,28 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
     kp.b_batched = B.batch_stride != 0;
     kp.amax_a = A.amax;
     kp.amax_b = B.amax;
+    kp.probe = g_gemm_probe;
     kp.status = device_status_ptr();
     if (!kp.status) {
         set_error("gemm_tf32x3: device status word unavailable");
         return AUSSM_ECUDA;
     }
     dim3 grid((s.M + BM - 1) / BM, (s.N + BN - 1) / BN, s.reduce_batches ? 1 : s.batches);
+    if (pair) {
+        grid.x = 2 * ((s.M + 255) / 256);       // clusters of two CTAs along M
+        if (half) {
+            if (A.mn_major)
+                return B.mn_major ? launch_pair<1, 1, true>(maps, kp, grid, stream)
+                                  : launch_pair<1, 0, true>(maps, kp, grid, stream);
+            return B.mn_major ? launch_pair<0, 1, true>(maps, kp, grid, stream)
+                              : launch_pair<0, 0, true>(maps, kp, grid, stream);
+        }
+        if (A.mn_major)
+            return B.mn_major ? launch_pair<1, 1, false>(maps, kp, grid, stream)
+                              : launch_pair<1, 0, false>(maps, kp, grid, stream);
+        return B.mn_major ? launch_pair<0, 1, false>(maps, kp, grid, stream)
+                          : launch_pair<0, 0, false>(maps, kp, grid, stream);
+    }
     if (half) {
         if (A.mn_major)
             return B.mn_major ? launch<1, 1, true>(maps, kp, grid, stream) : launch<1, 0, true>(maps, kp, grid, stream);

@@ -46,6 +46,11 @@ bool gemm_tf32x3_supported(const SplitOperand& A, const SplitOperand& B, const f
 int split_tf32(const float* src, long long ld_src, long long src_batch_stride, float* hi, float* lo, long long ld_dst,
                long long dst_batch_stride, long long rows, long long cols, int batches, cudaStream_t stream);
 
+// 1: clusters of two CTAs share the B tile (256 x 256 per pair); 0 (default): one CTA per 128 x 256 tile
+void set_gemm_pair(int on);
+// measurement only, results invalid: 1 skip the accumulator drain, 2 skip operand refills, 4 skip the MMAs
+void set_gemm_probe(int bits);
+
 // FP16 hi/lo split (see SplitOperand); amax is a device word that receives the bit pattern of max|src|
 int split_f16(const float* src, long long ld_src, long long src_batch_stride, void* hi, void* lo, long long ld_dst,
               long long dst_batch_stride, long long rows, long long cols, int batches, unsigned* amax,

@@ -53,7 +53,10 @@ const char* aussm_b200_last_error(void);
 int aussm_b200_device_status(aussm_stream_t stream);
 
 /* Tuning / measurement switches: name in {"fast_trig", "force_plain", "variant",
- * "gemm_tile"}.  Returns AUSSM_EINVAL for an unknown name. */
+ * "blocks_per_sm", "gemm_tile" (steps per time window of the drop-in operators),
+ * "gemm_backend" (0: tensor cores, FP16 parts where the pitches allow; 1: library
+ * SGEMM; 2: tensor cores, TF32 parts), "gemm_pair" (1: two-CTA tiles, 0: one CTA
+ * per tile, the default), "gemm_probe" (measurement only)}.  Returns AUSSM_EINVAL for an unknown name. */
 int aussm_b200_set_option(const char* name, int value);
 
 /* ---- scan core: the phase tensor theta is an input ----------------------

@@ -39,12 +39,15 @@ CASES = [
 ]
 
 
-@pytest.fixture(params=["f16", "tf32"])
+@pytest.fixture(params=["f16", "tf32", "f16-pair", "tf32-pair"])
 def parts(request):
-    """gemm_backend 0: FP16 parts where every pitch is a multiple of 8; 2: TF32 parts always"""
-    _lib.set_option("gemm_backend", 0 if request.param == "f16" else 2)
+    """gemm_backend 0: FP16 parts where every pitch is a multiple of 8; 2: TF32 parts always;
+    gemm_pair 0: one CTA per tile (default), 1: two-CTA tiles (tcgen05.mma.cta_group::2)"""
+    _lib.set_option("gemm_backend", 0 if request.param.startswith("f16") else 2)
+    _lib.set_option("gemm_pair", 1 if request.param.endswith("pair") else 0)
     yield request.param
     _lib.set_option("gemm_backend", 0)
+    _lib.set_option("gemm_pair", 0)
 
 
 @pytest.mark.parametrize("majors", [(0, 0), (0, 1), (1, 0), (1, 1)])
