@@ -28,6 +28,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 
@@ -73,6 +74,7 @@ struct GemmKernelParams {
     const unsigned* amax_a;   // FP16 parts: bit patterns of max|a|, max|b| (the parts are scaled by a power of two)
     const unsigned* amax_b;
     int probe;                // measurement only (results invalid): 1 no accumulator drain, 2 no refills, 4 no MMAs
+    int tiles_m, tiles_n, ntiles;   // one-CTA kernel: a CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 };
 
 // Power-of-two scale that brings a tensor whose largest magnitude has the bit pattern `maxbits` to about 2^14
@@ -218,8 +220,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-    const int zb = blockIdx.z;                                  // independent batch entry (0 when reducing)
+    // Persistent CTA: tile t -> (row block fastest, then column block, then independent batch entry), so that CTAs
+    // running side by side share a B tile in L2.  Barrier phases, stage indices and chunk counters run on across
+    // tiles: the copies and MMAs of the next tile start while the epilogue warps still store the previous one.
+    const int tiles_mn = p.tiles_m * p.tiles_n;
     constexpr int BK = HALF ? 64 : 32;                         // K values per block
     constexpr int MNBOX = HALF ? 64 : 32;                      // row elements per MN-major TMA box
     constexpr int MNBOX_BYTES = MNBOX * BK_BYTES;
@@ -252,11 +256,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     if (warp == 0) {
         if (lane == 0) {
             // ---- TMA producer ----
-            for (int it = 0; it < total; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
-                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, p.status)) { failed = 1; break; }
-                if ((p.probe & 2) && it >= PROBE_STAGES) {       // stale operands: no traffic from L2
+            int g = 0;                                   // K blocks copied by this CTA so far
+            bool okp = true;
+            for (int t = blockIdx.x; t < p.ntiles && okp; t += gridDim.x) {
+            const int zb = t / tiles_mn, m0 = ((t % tiles_mn) % p.tiles_m) * BM, n0 = ((t % tiles_mn) / p.tiles_m) * BN;
+            for (int it = 0; it < total; ++it, ++g) {
+                const int s = g % STAGES;
+                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, p.status)) { failed = 1; okp = false; break; }
+                if ((p.probe & 2) && g >= PROBE_STAGES) {        // stale operands: no traffic from L2
                     if (PROBE_LEADER) mbar_arrive(&full_bar[s]);
                     continue;
                 }
@@ -291,6 +299,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                     tma_load_3d(b_lo, &mapB_lo, &full_bar[s], k0, n0, bb);
                 }
             }
+            }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -298,9 +307,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
             constexpr uint32_t idesc = instr_desc<A_MN, B_MN, HALF>();
             bool ok = true;
             int ch[2] = {0, 0};                       // chunks finished per column half
-            for (int it = 0; it < total && ok; ++it) {
-                const int s = it % STAGES;
-                if (!mbar_wait_bounded(&full_bar[s], (uint32_t)(it / STAGES) & 1u, p.status)) { failed = 1; ok = false; break; }
+            int g = 0;                                // K blocks consumed so far
+            for (int t = blockIdx.x; t < p.ntiles && ok; t += gridDim.x)
+            for (int it = 0; it < total && ok; ++it, ++g) {
+                const int s = g % STAGES;
+                if (!mbar_wait_bounded(&full_bar[s], (uint32_t)(g / STAGES) & 1u, p.status)) { failed = 1; ok = false; break; }
                 tc_fence_after();
                 const uint32_t st = smem_addr(smem + s * STAGE_BYTES);
                 const uint32_t a_hi = st, a_lo = st + A_TILE_BYTES;
@@ -338,8 +349,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
         const int quarter = warp & 3;
         const int slice = (warp - 2) >> 2;
         float acc[2][64];                        // scaled units (FP16 parts): the scales come off once, at the end
-#pragma unroll
-        for (int i = 0; i < 64; ++i) acc[0][i] = acc[1][i] = 0.f;
         const float cross_scale = HALF ? pow2f(-LO_SHIFT) : 1.f;
         bool ok = true;
         int ch0 = 0, ch1 = 0;                            // chunks drained per column half
@@ -363,6 +372,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
             if (lane == 0) mbar_arrive(&acc_empty[h]);            // the issuer may start this half's next chunk
             ++chn;
         };
+        for (int t = blockIdx.x; t < p.ntiles; t += gridDim.x) {
+        const int zb = t / tiles_mn, m0 = ((t % tiles_mn) % p.tiles_m) * BM, n0 = ((t % tiles_mn) / p.tiles_m) * BN;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[0][i] = acc[1][i] = 0.f;
         for (int it = 0; it < total; ++it) {
             const int first = first_half(it, CHUNK_KB);
 #pragma unroll
@@ -405,6 +418,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                     }
                 }
             }
+        }
         }
     }
     tc_fence_before();
@@ -874,6 +888,17 @@ int launch_pair(const CUtensorMap* maps, const GemmKernelParams& kp, dim3 grid, 
 
 bool ok16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
 int g_gemm_pair = 0;     // option "gemm_pair": 1 = two-CTA kernel, 0 = one CTA per tile (default: measured equal or faster)
 int g_gemm_probe = 0;    // option "gemm_probe": knock-out switches for measurement (see GemmKernelParams)
 
@@ -922,6 +947,9 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
         return AUSSM_ECUDA;
     }
     dim3 grid((s.M + BM - 1) / BM, (s.N + BN - 1) / BN, s.reduce_batches ? 1 : s.batches);
+    kp.tiles_m = (int)grid.x;
+    kp.tiles_n = (int)grid.y;
+    kp.ntiles = (int)(grid.x * grid.y * grid.z);
     if (pair) {
         grid.x = 2 * ((s.M + 255) / 256);       // clusters of two CTAs along M
         if (half) {
@@ -937,6 +965,7 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
         return B.mn_major ? launch_pair<0, 1, false>(maps, kp, grid, stream)
                           : launch_pair<0, 0, false>(maps, kp, grid, stream);
     }
+    grid = dim3((unsigned)std::min(kp.ntiles, sm_count()), 1, 1);     // one persistent CTA per SM
     if (half) {
         if (A.mn_major)
             return B.mn_major ? launch<1, 1, true>(maps, kp, grid, stream) : launch<1, 0, true>(maps, kp, grid, stream);
