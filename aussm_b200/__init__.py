@@ -12,6 +12,7 @@ __version__ = "0.1.0"
 from .s6 import selective_scan_fn
 from .variants import project, scan_complex, ssm_adaptive_complex, ssm_adaptive_preal
 from .host import HostBatchStep
+from .linear import SplitLinear, split_linear
 
-__all__ = ["ops", "HostBatchStep", "selective_scan_fn", "scan_complex", "project", "ssm_adaptive_complex", "ssm_adaptive_preal", "ssm_adaptive_interface", "ssm_adaptive_unitary", "scan_unitary", "install_as_extension_cpp",
+__all__ = ["ops", "HostBatchStep", "SplitLinear", "split_linear", "selective_scan_fn", "scan_complex", "project", "ssm_adaptive_complex", "ssm_adaptive_preal", "ssm_adaptive_interface", "ssm_adaptive_unitary", "scan_unitary", "install_as_extension_cpp",
            "device_status"]

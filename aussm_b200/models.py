@@ -9,7 +9,9 @@ loads unchanged (ai-modules/wavesAI/model/aussm.py: ``SSMTS`` :100-227,
 :717-805, ``SSMauBlock`` :808-902, ``RMSNorm`` :905-916).  Only the scan calls
 differ: ``SSMauBlock`` calls ``aussm_b200.ops.ssm_adaptive_interface`` and
 ``MambaBlock`` calls ``aussm_b200.s6.selective_scan_fn`` (the reference imports
-the latter from the third-party package mamba-ssm).
+the latter from the third-party package mamba-ssm); and the ``nn.Linear``
+layers are ``aussm_b200.linear.SplitLinear`` (same parameters; the float32
+products run on the tensor cores through the library's split GEMM).
 """
 from __future__ import annotations
 
@@ -20,6 +22,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import ops, s6
+from .linear import SplitLinear, split_linear
 
 __all__ = ["RMSNorm", "SSMauBlock", "MambaBlock", "ResidualBlock", "SSMTS", "SSMSequenceClassifier"]
 
@@ -48,16 +51,16 @@ class SSMauBlock(nn.Module):
         super().__init__()
         self.d_model, self.d_state, self.use_conv = d_model, d_state, conv_1d
         dt_rank = d_state if dt_rank in (None, "auto") else dt_rank
-        self.in_proj = nn.Linear(d_model, 2 * d_model, bias=bias)
+        self.in_proj = SplitLinear(d_model, 2 * d_model, bias=bias)
         self.conv1d = nn.Conv1d(d_model, d_model, kernel_size=d_conv, groups=d_model, padding=d_conv - 1,
                                 bias=conv_bias)
-        self.out_proj = nn.Linear(d_model, d_model, bias=bias)
-        self.x_proj = nn.Linear(d_model, dt_rank, bias=False)
-        self.dt_proj = nn.Linear(dt_rank, d_model, bias=True)
+        self.out_proj = SplitLinear(d_model, d_model, bias=bias)
+        self.x_proj = SplitLinear(d_model, dt_rank, bias=False)
+        self.dt_proj = SplitLinear(dt_rank, d_model, bias=True)
         self.D = nn.Parameter(torch.ones(d_model))
         self.C = nn.Parameter(torch.randn(d_state, dtype=torch.complex64))
         self.B = nn.Parameter(torch.randn(d_state, dtype=torch.complex64))
-        self.xA_proj = nn.Linear(d_model, d_model * d_state, bias=True)
+        self.xA_proj = SplitLinear(d_model, d_model * d_state, bias=True)
         with torch.no_grad():
             self.xA_proj.bias.uniform_(-math.pi, math.pi)
 
@@ -87,12 +90,12 @@ class MambaBlock(nn.Module):
         self.d_model, self.d_state = d_model, d_state
         self.d_inner = int(expand * d_model)
         self.dt_rank = math.ceil(d_model / 16) if dt_rank in (None, "auto") else dt_rank
-        self.in_proj = nn.Linear(d_model, 2 * self.d_inner, bias=bias)
+        self.in_proj = SplitLinear(d_model, 2 * self.d_inner, bias=bias)
         self.conv1d = nn.Conv1d(self.d_inner, self.d_inner, kernel_size=d_conv, groups=self.d_inner,
                                 padding=d_conv - 1, bias=conv_bias)
-        self.out_proj = nn.Linear(self.d_inner, d_model, bias=bias)
-        self.x_proj = nn.Linear(self.d_inner, self.dt_rank + 2 * d_state, bias=False)
-        self.dt_proj = nn.Linear(self.dt_rank, self.d_inner, bias=True)
+        self.out_proj = SplitLinear(self.d_inner, d_model, bias=bias)
+        self.x_proj = SplitLinear(self.d_inner, self.dt_rank + 2 * d_state, bias=False)
+        self.dt_proj = SplitLinear(self.dt_rank, self.d_inner, bias=True)
         self.D = nn.Parameter(torch.ones(self.d_inner))
         self.A_log = nn.Parameter(torch.log(torch.arange(1, d_state + 1, dtype=torch.float32)).repeat(self.d_inner, 1))
         self.A_log._no_weight_decay = True
@@ -143,11 +146,11 @@ class SSMTS(nn.Module):
                  mamba_expand: int = 2, dt_rank="auto", d_conv: int = 4, conv_bias: bool = True, bias: bool = False,
                  ssmau_conv_1d: bool = True):
         super().__init__()
-        self.embedding = nn.Linear(input_dim, d_model)
+        self.embedding = SplitLinear(input_dim, d_model)
         self.layers = _build_layers(layers, d_model, d_state, mamba_expand, dt_rank, d_conv, conv_bias, bias,
                                     ssmau_conv_1d)
         self.norm_f = RMSNorm(d_model)
-        self.output = nn.Linear(d_model, output_dim, bias=False)
+        self.output = SplitLinear(d_model, output_dim, bias=False)
 
     def forward(self, x):
         x = self.embedding(x)
@@ -168,7 +171,7 @@ class SSMSequenceClassifier(nn.Module):
         self.layers = _build_layers(layers, d_model, d_state, mamba_expand, dt_rank, d_conv, conv_bias, bias,
                                     ssmau_conv_1d)
         self.norm_f = RMSNorm(d_model)
-        self.output = nn.Linear(d_model, output_dim, bias=False)
+        self.output = SplitLinear(d_model, output_dim, bias=False)
 
     def forward(self, input_ids, lengths=None):
         x = self.embedding(input_ids)

@@ -3,6 +3,7 @@ modules evaluated on the CPU in float64 with the oracle's scans substituted for 
 import pytest
 import torch
 
+import aussm_b200
 from aussm_b200 import models, ops, s6
 from aussm_b200.train import make_config, train_step
 from oracle import unitary as OU
@@ -90,3 +91,30 @@ def test_training_step_runs_and_reduces_the_loss(config):
     for _ in range(8):
         last, _ = train_step(model, opt, x, y, loss_fn, 1, micro_batch=2)
     assert last < first
+
+
+@pytest.mark.parametrize("shape", [(3, 50, 64, 128), (2, 7, 128, 36), (1, 1, 16, 8), (4, 33, 21, 128),
+                                   (8, 2048, 64, 256)])
+def test_split_linear_matches_float64(shape, monkeypatch):
+    """SplitLinear == F.linear in float64 (forward and both gradients); sizes that are not multiples of 4 fall back;
+    the last shape cuts the weight gradient's long contraction into slices."""
+    import torch.nn.functional as F
+    from aussm_b200 import linear
+    from aussm_b200.linear import split_linear
+    monkeypatch.setattr(linear, "MIN_FLOP", 0.0)
+    b, l, d_in, d_out = shape
+    gen = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(b, l, d_in, generator=gen)
+    w = torch.randn(d_out, d_in, generator=gen) / d_in ** 0.5
+    bias = torch.randn(d_out, generator=gen)
+    gy = torch.randn(b, l, d_out, generator=gen)
+    xs = [t.cuda().requires_grad_(True) for t in (x, w, bias)]
+    y = split_linear(*xs)
+    y.backward(gy.cuda())
+    xd = [t.double().requires_grad_(True) for t in (x, w, bias)]
+    yd = F.linear(*xd)
+    yd.backward(gy.double())
+    assert aussm_b200.device_status() == 0
+    for name, got, want in [("y", y, yd)] + [(n, a.grad, c.grad) for n, a, c in zip(("x", "w", "b"), xs, xd)]:
+        err = (got.detach().cpu().double() - want.detach()).abs().max().item()
+        assert err <= 3e-6 * max(1.0, want.abs().max().item()), (name, err)
