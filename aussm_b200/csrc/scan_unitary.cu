@@ -971,6 +971,7 @@ cudaError_t launch_scan_unitary_fwd(const ScanFwdParams& p_, cudaStream_t stream
         if (o.variant == 7) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 1>>(p, async, fast, stream);
         if (o.variant == 8) return launch_fwd_sel<FwdCfg<8, 2, 16, 2, 2>>(p, async, fast, stream);
         if (o.variant == 9) return launch_fwd_sel<FwdCfg<8, 2, 16, 3, 2>>(p, async, fast, stream);
+        if (o.variant == 10) return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 1>>(p, async, fast, stream);
         return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 4>>(p, async, fast, stream);
     }
     if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 32, 2, 4>>(p, async, fast, stream);
