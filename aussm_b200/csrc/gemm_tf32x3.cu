@@ -45,6 +45,7 @@ constexpr int BK_BYTES = 128;                        // one K block = one 128-by
 constexpr int STAGES = 2;
 constexpr int A_TILE_BYTES = BM * BK_BYTES;          // 16 KB
 constexpr int B_TILE_BYTES = BN * BK_BYTES;          // 32 KB
+constexpr int B_HALF_BYTES = 128 * BK_BYTES;         // one part of one 128-column half: 16 KB
 constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // hi + lo of both operands: 96 KB
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + slack for 1024-byte alignment
 // Tensor-memory accumulation truncates instead of rounding, so a long K loop drifts (measured 3.5e-5 relative
@@ -275,7 +276,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                 uint8_t* a_hi = st;
                 uint8_t* a_lo = st + A_TILE_BYTES;
                 uint8_t* b_hi = st + 2 * A_TILE_BYTES;
-                uint8_t* b_lo = st + 2 * A_TILE_BYTES + B_TILE_BYTES;
                 mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
                 const int k0 = kb * BK;
                 if (A_MN) {
@@ -288,15 +288,23 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                     tma_load_3d(a_hi, &mapA_hi, &full_bar[s], k0, m0, ba);
                     tma_load_3d(a_lo, &mapA_lo, &full_bar[s], k0, m0, ba);
                 }
-                if (B_MN) {
+                // B: per 128-column half the hi rows and then the lo rows, so that one N = 256 descriptor covers
+                // [b_hi | b_lo] of a half
 #pragma unroll
-                    for (int i = 0; i < BN / MNBOX; ++i) {
-                        tma_load_3d(b_hi + i * MNBOX_BYTES, &mapB_hi, &full_bar[s], n0 + MNBOX * i, k0, bb);
-                        tma_load_3d(b_lo + i * MNBOX_BYTES, &mapB_lo, &full_bar[s], n0 + MNBOX * i, k0, bb);
+                for (int h = 0; h < 2; ++h) {
+                    uint8_t* bh = b_hi + h * 2 * B_HALF_BYTES;
+                    uint8_t* bl = bh + B_HALF_BYTES;
+                    const int nb = n0 + h * MMA_N;
+                    if (B_MN) {
+#pragma unroll
+                        for (int i = 0; i < MMA_N / MNBOX; ++i) {
+                            tma_load_3d(bh + i * MNBOX_BYTES, &mapB_hi, &full_bar[s], nb + MNBOX * i, k0, bb);
+                            tma_load_3d(bl + i * MNBOX_BYTES, &mapB_lo, &full_bar[s], nb + MNBOX * i, k0, bb);
+                        }
+                    } else {
+                        tma_load_3d(bh, &mapB_hi, &full_bar[s], k0, nb, bb);
+                        tma_load_3d(bl, &mapB_lo, &full_bar[s], k0, nb, bb);
                     }
-                } else {
-                    tma_load_3d(b_hi, &mapB_hi, &full_bar[s], k0, n0, bb);
-                    tma_load_3d(b_lo, &mapB_lo, &full_bar[s], k0, n0, bb);
                 }
             }
             }
@@ -304,7 +312,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer: per chunk of CHUNK_KB K-blocks, column half 0 then column half 1 ----
-            constexpr uint32_t idesc = instr_desc<A_MN, B_MN, HALF>();
+            constexpr uint32_t idesc = instr_desc<A_MN, B_MN, HALF>();                        // N = 128
+            constexpr uint32_t idesc2 = idesc + ((uint32_t)(MMA_N >> 3) << 17);               // N = 256
             bool ok = true;
             int ch[2] = {0, 0};                       // chunks finished per column half
             int g = 0;                                // K blocks consumed so far
@@ -325,15 +334,16 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                         tc_fence_after();
                     }
                     const uint32_t acc_main = tmem_base + (uint32_t)(h * 2 * MMA_N), acc_cross = acc_main + MMA_N;
-                    const uint32_t b_hi = st + 2 * A_TILE_BYTES + h * (MMA_N * BK_BYTES), b_lo = b_hi + B_TILE_BYTES;
+                    // [b_hi | b_lo] of this half are adjacent: a_hi meets both in one N = 256 instruction whose
+                    // output columns are [main | cross] (one read of a_hi instead of two), then a_lo * b_hi
+                    const uint32_t b_hi = st + 2 * A_TILE_BYTES + h * 2 * B_HALF_BYTES;
                     if (!(p.probe & 4))
 #pragma unroll
                     for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
                         const uint64_t ah = operand_desc<A_MN, HALF>(a_hi, kk), al = operand_desc<A_MN, HALF>(a_lo, kk);
-                        const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk), bl = operand_desc<B_MN, HALF>(b_lo, kk);
+                        const uint64_t bh = operand_desc<B_MN, HALF>(b_hi, kk);
                         const uint32_t acc_flag = (starts && kk == 0) ? 0u : 1u;
-                        if (HALF) umma_f16(acc_main, ah, bh, idesc, acc_flag); else umma_tf32(acc_main, ah, bh, idesc, acc_flag);
-                        if (HALF) umma_f16(acc_cross, ah, bl, idesc, acc_flag); else umma_tf32(acc_cross, ah, bl, idesc, acc_flag);
+                        if (HALF) umma_f16(acc_main, ah, bh, idesc2, acc_flag); else umma_tf32(acc_main, ah, bh, idesc2, acc_flag);
                         if (HALF) umma_f16(acc_cross, al, bh, idesc, 1u); else umma_tf32(acc_cross, al, bh, idesc, 1u);
                     }
                     if (half_ends(h, it, total, CHUNK_KB)) {
@@ -928,7 +938,7 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
     if (int rc = make_map(&maps[0], A.hi, half, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
     if (int rc = make_map(&maps[1], A.lo, half, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
     const bool pair = g_gemm_pair != 0;
-    const int b_box_rows = pair ? 64 : BN;     // K-major B: a CTA of a pair copies 64 rows per column half
+    const int b_box_rows = pair ? 64 : 128;    // K-major B: one part of a column half per copy (64 rows per CTA of a pair)
     if (int rc = make_map(&maps[2], B.hi, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, b_box_rows)) return rc;
     if (int rc = make_map(&maps[3], B.lo, half, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, b_box_rows)) return rc;
     GemmKernelParams kp;
