@@ -174,7 +174,7 @@ __device__ __forceinline__ int slot_of(int c, int j) {
 // of every 16-byte piece this lane copies per tile (at step 0 of the launch).
 template <class C>
 struct TileMap {
-    unsigned theta_off[C::NCH_THETA];     // float offset from the warp's first theta row
+    unsigned theta_off[C::NCH_THETA];     // byte offset from the warp's first theta row (32 bits: base + offset addressing)
     const float* aux_ptr[C::NCH_AUX];     // per-channel rows (nullptr: this lane has no piece)
 
     __device__ __forceinline__ void init(int lane, int nvalid, int N, long long ld_theta, long long ld_row,
@@ -187,7 +187,7 @@ struct TileMap {
             const int c = w / C::NL, j = (w % C::NL) + k * C::NL;
             const bool ok = c < nvalid && j < N;
             const long long row = ok ? (long long)c * N + j : 0;      // missing rows shadow row 0
-            theta_off[i] = (unsigned)(row * ld_theta + col * 4);
+            theta_off[i] = (unsigned)((row * ld_theta + col * 4) * (long long)sizeof(float));
         }
 #pragma unroll
         for (int i = 0; i < C::NCH_AUX; ++i) {
@@ -215,7 +215,8 @@ struct TileMap {
 #pragma unroll
         for (int i = 0; i < C::NCH_THETA; ++i) {
             if (FULL || col * 4 < tlen)
-                cp_async16_s(dst0 + (uint32_t)(i * RPI * C::TP * sizeof(float)), theta_t0 + theta_off[i]);
+                cp_async16_s(dst0 + (uint32_t)(i * RPI * C::TP * sizeof(float)),
+                             reinterpret_cast<const char*>(theta_t0) + theta_off[i]);
         }
         const uint32_t aux0 = smem_addr(stage) +
                               (uint32_t)((C::NROWS * C::TP + (lane / CPR) * C::T + col * 4) * sizeof(float));
@@ -717,7 +718,8 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
             if (nvalid == C::CPW && N == NL * SPT && tlen == T) {      // whole tile, every row real: no per-piece test
 #pragma unroll
                 for (int i = 0; i < C::NCH_THETA; ++i)
-                    *reinterpret_cast<float4*>(dst0 + map.theta_off[i]) = ld_shared_f4(src0 + i * RPI * TP);
+                    *reinterpret_cast<float4*>(reinterpret_cast<char*>(dst0) + map.theta_off[i]) =
+                            ld_shared_f4(src0 + i * RPI * TP);
             } else {
 #pragma unroll
                 for (int i = 0; i < C::NCH_THETA; ++i) {
@@ -725,7 +727,8 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
                     const int k = slot / 32, w = slot % 32;
                     const bool real_row = (w / NL) < nvalid && ((w % NL) + k * NL) < N;
                     if (real_row && col * 4 < tlen)
-                        *reinterpret_cast<float4*>(dst0 + map.theta_off[i]) = ld_shared_f4(src0 + i * RPI * TP);
+                        *reinterpret_cast<float4*>(reinterpret_cast<char*>(dst0) + map.theta_off[i]) =
+                            ld_shared_f4(src0 + i * RPI * TP);
                 }
             }
             __syncwarp();
@@ -941,8 +944,8 @@ cudaError_t launch_bwd_sel(const ScanBwdParams& p, bool async, bool fast, cudaSt
     return bias ? launch_bwd_cfg<C, true, false, true>(p, s) : launch_bwd_cfg<C, true, false, false>(p, s);
 }
 
-// a warp's rows must be addressable with 32-bit float offsets from its first row
-inline bool offsets_fit(long long ld, int rows_per_warp) { return ld * (long long)rows_per_warp < (1LL << 31); }
+// a warp's rows must be addressable with 32-bit byte offsets from its first row
+inline bool offsets_fit(long long ld, int rows_per_warp) { return ld * (long long)rows_per_warp < (1LL << 29); }
 
 }  // namespace
 
