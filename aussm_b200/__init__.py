@@ -11,7 +11,7 @@ from .ops import (device_status, install_as_extension_cpp, scan_unitary, ssm_ada
 __version__ = "0.1.0"
 from .s6 import selective_scan_fn
 from .variants import project, scan_complex, ssm_adaptive_complex, ssm_adaptive_preal
-from .host import HostBatchStep
+from .host import HostBatchStep, bind_process_to_gpu_cpus
 from .linear import SplitLinear, split_linear
 
 __all__ = ["ops", "HostBatchStep", "SplitLinear", "split_linear", "selective_scan_fn", "scan_complex", "project", "ssm_adaptive_complex", "ssm_adaptive_preal", "ssm_adaptive_interface", "ssm_adaptive_unitary", "scan_unitary", "install_as_extension_cpp",

@@ -25,7 +25,36 @@ from torch import Tensor
 
 from . import ops
 
-__all__ = ["HostBatchStep"]
+__all__ = ["HostBatchStep", "bind_process_to_gpu_cpus"]
+
+
+def bind_process_to_gpu_cpus(device) -> int:
+    """Restrict the calling process to the CPU cores next to `device` (NVML's ideal CPU affinity of that GPU), so that
+    pinned host buffers allocated afterwards land on the GPU's own NUMA node.  With one process per GPU on a
+    two-socket host this keeps the host<->device copies of all ranks off the inter-socket link.  Returns the number
+    of cores in the new affinity set, or 0 if nothing was changed (NVML missing, no affinity information)."""
+    import os
+    try:
+        import pynvml
+        dev = torch.device(device)
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(idx).uuid)
+            handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        except Exception:
+            handle = pynvml.nvmlDeviceGetHandleByIndex(idx)
+        ncpu = os.cpu_count() or 1
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (ncpu + 63) // 64)
+        cpus = {64 * w + b for w, mask in enumerate(words) for b in range(64) if (int(mask) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        cpus &= allowed
+        if not cpus or cpus == allowed:
+            return 0
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return 0
 
 _SEQ = ("u", "dt", "z", "gy")                    # (b, d, l) tensors that travel per chunk
 _PARAMS = ("x", "x_bias", "B", "C", "D")

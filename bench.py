@@ -334,10 +334,14 @@ def run_e2e(args, dev, world, rank):
     import aussm_b200
 
     b, d, n, l = args.batch, args.d_inner, args.d_state, args.seq_len
+    # pinned buffers on the GPU's own NUMA node (matters when several ranks share a two-socket host)
+    saved_affinity = os.sched_getaffinity(0)
     host = make_op_inputs_cpu(b, d, n, l, 4321 + rank)
+    numa_cpus = aussm_b200.bind_process_to_gpu_cpus(dev)
     pin = {k: v.pin_memory() for k, v in host.items()}
     out_host = {k: torch.empty_like(v).pin_memory() for k, v in host.items() if k != "gy"}
     out_host["y"] = torch.empty_like(host["u"]).pin_memory()
+    os.sched_setaffinity(0, saved_affinity)          # only the allocations above needed the binding
     h2d = sum(v.numel() * v.element_size() for v in pin.values())
     d2h = sum(v.numel() * v.element_size() for v in out_host.values())
 
@@ -368,6 +372,7 @@ def run_e2e(args, dev, world, rank):
     elems = b * d * n * l * world
     return {"value": elems / (float(ms.item()) * 1e-3) / 1e9, "unit": "Gelem/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h, "ms_per_step": float(ms.item()), "steps": steps,
+            "host_cpus_bound": numa_cpus,
             "api": "aussm_b200.HostBatchStep (chunks of batch/8 through ssm_adaptive_interface, the extension_cpp "
                    "drop-in; three-stream copy-in / compute / copy-out pipeline), host pinned buffers",
             "gpu_launches_per_step": "per chunk and window: 3 tcgen05 GEMMs, 3 TF32 splits, 1 fwd + 1 bwd scan; "
