@@ -70,9 +70,10 @@ class HostBatchStep:
     stream waits for the last copy, so a synchronize (or an event recorded on it) covers the whole step.
     """
 
-    def __init__(self, device, chunk: Optional[int] = None):
+    def __init__(self, device, chunk: Optional[int] = None, short_edges: bool = True):
         self.device = torch.device(device)
         self.chunk = chunk
+        self.short_edges = short_edges
         self.s_in = torch.cuda.Stream(self.device)
         self.s_cmp = torch.cuda.Stream(self.device)
         self.s_out = torch.cuda.Stream(self.device)
@@ -102,11 +103,20 @@ class HostBatchStep:
         with torch.cuda.stream(self.s_cmp):
             params = [inputs[k].to(self.device, non_blocking=True).detach().requires_grad_(True) for k in _PARAMS]
 
-        nchunks = (b + chunk - 1) // chunk
+        # chunk boundaries: a short first and last chunk (the copy-in of the first and the copy-out of the last are
+        # the two transfers nothing can hide)
+        edge = 1 if (chunk >= 2 and b >= 2 * chunk + 2 and self.short_edges) else 0
+        bounds = [0]
+        if edge:
+            bounds.append(edge)
+        while bounds[-1] < b - edge:
+            bounds.append(min(b - edge, bounds[-1] + chunk))
+        if edge:
+            bounds.append(b)
         in_ready = [None, None]       # copy-in of the chunk in buffer set i is complete
         in_free = [None, None]        # the compute stream no longer reads buffer set i
-        for c in range(nchunks):
-            lo, hi = c * chunk, min(b, (c + 1) * chunk)
+        for c in range(len(bounds) - 1):
+            lo, hi = bounds[c], bounds[c + 1]
             i = c % 2
             buf = self._bufs[i]
             with torch.cuda.stream(self.s_in):
