@@ -42,10 +42,6 @@
 #include "common.cuh"
 #include "scan_unitary.cuh"
 
-#ifndef AUSSM_PROBE
-#define AUSSM_PROBE 0
-#endif
-
 namespace aussm {
 
 __device__ int g_device_status = 0;
@@ -320,7 +316,7 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
 
         // pre-pass: v = silu(u) over the u row, s = dt * v over the dt row
 #pragma unroll
-        for (int it = 0; it < ((AUSSM_PROBE & 4) ? 0 : C::ITERS); ++it) {
+        for (int it = 0; it < C::ITERS; ++it) {
             const int e0 = (lane + 32 * it) * VW;
             const int cc = e0 / T, t = e0 % T;
             if (t < tlen) {
@@ -385,7 +381,7 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
         __syncwarp();
 
         // post-pass: one lane = one channel and VW steps
-        if (p.y && !(AUSSM_PROBE & 2)) {
+        if (p.y) {
 #pragma unroll
             for (int it = 0; it < C::ITERS; ++it) {
                 const int e0 = (lane + 32 * it) * VW;
@@ -416,12 +412,8 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
         __syncwarp();
         if (ASYNC) {
             const int nt = tile + STAGES;
-#if (AUSSM_PROBE & 1)
-            cp_async_commit();
-#else
             if (nt < ntiles) map.issue(th, theta_warp, (long long)nt * T, min(T, L - nt * T), lane);
             else cp_async_commit();
-#endif
         }
     }
     if (ASYNC) cp_async_wait<0>();
@@ -968,13 +960,6 @@ cudaError_t launch_scan_unitary_fwd(const ScanFwdParams& p_, cudaStream_t stream
         if (o.variant == 1) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 4>>(p, async, fast, stream);
         if (o.variant == 2) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 4>>(p, async, fast, stream);
         if (o.variant == 3) return launch_fwd_sel<FwdCfg<16, 1, 32, 3, 4>>(p, async, fast, stream);
-        if (o.variant == 4) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 2>>(p, async, fast, stream);
-        if (o.variant == 5) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 1>>(p, async, fast, stream);
-        if (o.variant == 6) return launch_fwd_sel<FwdCfg<4, 4, 32, 2, 1>>(p, async, fast, stream);
-        if (o.variant == 7) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 1>>(p, async, fast, stream);
-        if (o.variant == 8) return launch_fwd_sel<FwdCfg<8, 2, 16, 2, 2>>(p, async, fast, stream);
-        if (o.variant == 9) return launch_fwd_sel<FwdCfg<8, 2, 16, 3, 2>>(p, async, fast, stream);
-        if (o.variant == 10) return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 1>>(p, async, fast, stream);
         return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 4>>(p, async, fast, stream);
     }
     if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 32, 2, 4>>(p, async, fast, stream);
@@ -1002,8 +987,6 @@ cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p_, cudaStream_t stream
         if (o.variant == 1) return launch_bwd_sel<BwdCfg<8, 2, 32, 32, 2, 2>>(p, async, fast, stream);
         if (o.variant == 2) return launch_bwd_sel<BwdCfg<16, 1, 64, 32, 2, 2>>(p, async, fast, stream);
         if (o.variant == 3) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 3, 2>>(p, async, fast, stream);
-        if (o.variant == 8) return launch_bwd_sel<BwdCfg<8, 2, 16, 16, 2, 1>>(p, async, fast, stream);
-        if (o.variant == 9) return launch_bwd_sel<BwdCfg<8, 2, 16, 16, 3, 1>>(p, async, fast, stream);
 
         // one-warp blocks: a finished warp is replaced at once (measured 9.55 ms against 10.2 ms with two-warp blocks)
         return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 1>>(p, async, fast, stream);
