@@ -464,9 +464,16 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
         p.accumulate = first ? 0 : 1;
         p.nch = (int)nch; p.Dmod = D; p.N = N; p.L = tl;
         p.ld_theta = pl.ldw; p.ld_dtheta = pl.ldw; p.ld_row = L;
+        // the scan leaves max|dtheta| of the window behind for the FP16 split of the adjoint GEMMs
+        const bool fused_amax = ps.use_tensor_cores && ps.half;
+        if (fused_amax) {
+            cudaError_t em = cudaMemsetAsync(ps.amax + 2, 0, sizeof(unsigned), stream);
+            if (em != cudaSuccess) return cuda_fail(em, "clearing the dtheta maximum");
+            p.dtheta_amax = ps.amax + 2;
+        }
         cudaError_t e = launch_scan_unitary_bwd(p, stream);
         if (e != cudaSuccess) return cuda_fail(e, "unitary scan backward launch");
-        if (int rc = proj_adjoints(pd, theta_w, x, u, dx, du, first, ps, stream)) return rc;
+        if (int rc = proj_adjoints(pd, theta_w, x, u, dx, du, first, ps, stream, fused_amax)) return rc;
     }
     ReduceParams r = {};
     r.part_bc = part_bc; r.part_d = part_d; r.part_rowsum = part_rowsum;

@@ -988,18 +988,19 @@ int gemm_tf32x3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
 
 int split_f16(const float* src, long long ld_src, long long src_batch_stride, void* hi, void* lo, long long ld_dst,
               long long dst_batch_stride, long long rows, long long cols, int batches, unsigned* amax,
-              cudaStream_t stream) {
+              cudaStream_t stream, bool have_amax) {
     if (cols % 4 || ld_src % 4 || ld_dst % 8 || dst_batch_stride % 8 || !ok16(src) || !ok16(hi) || !ok16(lo) || !amax) {
         set_error("split_f16: rows must be 16-byte aligned (cols=%lld ld_src=%lld ld_dst=%lld)", cols, ld_src, ld_dst);
         return AUSSM_EINVAL;
     }
     const long long total = rows * (cols / 4);
     if (total <= 0 || batches <= 0) return AUSSM_OK;
-    cudaError_t e = cudaMemsetAsync(amax, 0, sizeof(unsigned), stream);
+    cudaError_t e = have_amax ? cudaSuccess : cudaMemsetAsync(amax, 0, sizeof(unsigned), stream);
     if (e == cudaSuccess) {
         const unsigned blocks = (unsigned)std::min<long long>((total + 255) / 256, 148 * 8);
-        absmax_kernel<<<dim3(blocks, 1, batches), 256, 0, stream>>>(src, ld_src, src_batch_stride, rows, cols / 4,
-                                                                    amax);
+        if (!have_amax)
+            absmax_kernel<<<dim3(blocks, 1, batches), 256, 0, stream>>>(src, ld_src, src_batch_stride, rows, cols / 4,
+                                                                        amax);
         split_f16_kernel<<<dim3(std::min<unsigned>(blocks * 2, 148 * 16), 1, batches), 256, 0, stream>>>(
             src, ld_src, src_batch_stride, static_cast<__half*>(hi), static_cast<__half*>(lo), ld_dst,
             dst_batch_stride, rows, cols / 4, amax);

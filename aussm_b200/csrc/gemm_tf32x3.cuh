@@ -52,8 +52,9 @@ void set_gemm_pair(int on);
 void set_gemm_probe(int bits);
 
 // FP16 hi/lo split (see SplitOperand); amax is a device word that receives the bit pattern of max|src|
+// have_amax: *amax already holds the maximum (its producer computed it): the pass over src is skipped
 int split_f16(const float* src, long long ld_src, long long src_batch_stride, void* hi, void* lo, long long ld_dst,
               long long dst_batch_stride, long long rows, long long cols, int batches, unsigned* amax,
-              cudaStream_t stream);
+              cudaStream_t stream, bool have_amax = false);
 
 }  // namespace aussm

@@ -166,7 +166,7 @@ int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w
 }
 
 int proj_adjoints(const ProjDims& d, const float* dtheta_w, const float* x, const float* u, float* dx, float* du,
-                  bool overwrite_dx, ProjScratch& s, cudaStream_t stream) {
+                  bool overwrite_dx, ProjScratch& s, cudaStream_t stream, bool dtheta_amax_known) {
     if (!s.use_tensor_cores) {
         if (int rc = lib_dx(d, dtheta_w, u, dx, overwrite_dx, stream)) return rc;
         return lib_du(d, dtheta_w, x, du, stream);
@@ -174,7 +174,7 @@ int proj_adjoints(const ProjDims& d, const float* dtheta_w, const float* x, cons
     const int M = d.D * d.N;
     if (s.half) {
         if (int rc = split_f16(dtheta_w, d.ldw, (long long)M * d.ldw, s.dth_hi, s.dth_lo, d.ldw, (long long)M * d.ldw,
-                               M, d.tl, d.B, s.amax + 2, stream))
+                               M, d.tl, d.B, s.amax + 2, stream, dtheta_amax_known))
             return rc;
     } else if (int rc = split_tf32(dtheta_w, d.ldw, (long long)M * d.ldw, s.dth_hi, s.dth_lo, d.ldw,
                                    (long long)M * d.ldw, M, d.tl, d.B, stream)) {

@@ -51,8 +51,9 @@ int proj_split_u(const ProjDims& d, const float* u, ProjScratch& s, cudaStream_t
 int proj_theta(const ProjDims& d, const float* x, const float* u, float* theta_w, ProjScratch& s,
                cudaStream_t stream);
 // dx and du from dtheta_w; requires proj_theta() to have run on the same window (it leaves u's split behind)
+// dtheta_amax_known: s.amax[2] already holds the bit pattern of max|dtheta_w| (the scan kernel produced it)
 int proj_adjoints(const ProjDims& d, const float* dtheta_w, const float* x, const float* u, float* dx, float* du,
-                  bool overwrite_dx, ProjScratch& s, cudaStream_t stream);
+                  bool overwrite_dx, ProjScratch& s, cudaStream_t stream, bool dtheta_amax_known = false);
 
 void set_error(const char* fmt, ...);
 void set_gemm_backend(int mode);   // 0: tensor cores, FP16 parts when the pitches allow; 1: library SGEMM; 2: TF32 parts

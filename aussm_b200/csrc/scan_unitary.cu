@@ -490,6 +490,7 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
     float er[SPT], ei[SPT];     // exp(-i theta_{t+1}) eta_{t+1}
     float gmr[SPT], gmi[SPT];   // sum_t w_t conj(h_t)
     float sbr[SPT], sbi[SPT];   // sum_t eta_t s_t              (general representation only)
+    float amax = 0.f;           // max |dtheta| seen by this thread (drop-in pipeline: spares the GEMM's own pass)
     float rsum[SPT];            // sum_t dtheta_t
     float hlr[SPT], hli[SPT];   // conj(h_{L-1}) . gh   (boundary term of the Bc gradient)
 #pragma unroll
@@ -622,7 +623,7 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
                         // dtheta_t = -Im(conj(eta) a)
                         const float d = fmaf(ni, ar, -nr * ai);
                         dth[e] = d;
-                        if (BIAS) rsum[k] += d;
+                        if (BIAS) { rsum[k] += d; amax = fmaxf(amax, fabsf(d)); }
                         const float pv = fmaf(sc[k].mr, hr[k], -sc[k].mi * hi[k]);
                         // gradient of the real drive s_t: Re(conj(eta) beta)
                         const float ev = NORM ? nr : fmaf(nr, sc[k].br, ni * sc[k].bi);
@@ -777,6 +778,11 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
         if (BIAS && p.part_rowsum) p.part_rowsum[o] = rsum[k] + (p.accumulate ? p.part_rowsum[o] : 0.f);
         if (p.dh0_re) { p.dh0_re[o] = d0r; p.dh0_im[o] = d0i; }
         if (p.h0_re) { p.h0_re[o] = s0r; p.h0_im[o] = s0i; }
+    }
+    if (BIAS && p.dtheta_amax) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (lane == 0 && amax > 0.f) atomicMax(p.dtheta_amax, __float_as_uint(fminf(amax, 3.0e38f)));
     }
     // dD: add the lanes' partial sums channel by channel through the scratch tile
     __syncwarp();

@@ -61,6 +61,8 @@ struct ScanBwdParams {
     float* part_bc;            // (nch, N, 4): grad of Bc (re, im), grad of Cc (re, im)
     float* part_d;             // (nch,)
     float* part_rowsum;        // (nch, N) sum over t of dtheta, or nullptr
+    unsigned* dtheta_amax;     // receives (atomic max) the bit pattern of max|dtheta| of this launch, or nullptr;
+                               // only with theta_bias / part_rowsum given (the drop-in pipeline)
     int accumulate;            // 1: add to the partial buffers instead of overwriting them
     int nch, Dmod, N, L;
     long long ld_theta;

@@ -51,6 +51,7 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=WORKLOAD["seq_len"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-chunk", type=int, default=0, help="batch entries per pipeline chunk of the e2e leg (0: batch/8)")
+    ap.add_argument("--e2e-streams", type=int, default=1, help="compute streams of the e2e pipeline (1 or 2)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--fast-trig", type=int, default=0)
     ap.add_argument("--variant", type=int, default=0)
@@ -345,7 +346,7 @@ def run_e2e(args, dev, world, rank):
     h2d = sum(v.numel() * v.element_size() for v in pin.values())
     d2h = sum(v.numel() * v.element_size() for v in out_host.values())
 
-    pipe = aussm_b200.HostBatchStep(dev, chunk=args.e2e_chunk or None)
+    pipe = aussm_b200.HostBatchStep(dev, chunk=args.e2e_chunk or None, compute_streams=args.e2e_streams)
 
     def step():
         pipe.step(pin, out_host)
