@@ -36,7 +36,7 @@ def test_workspace_queries_and_options():
     # the window workspace is bounded: it does not grow with the sequence length
     a = lib.aussm_b200_unitary_workspace_bytes(16, 1024, 16, 16384)
     b = lib.aussm_b200_unitary_workspace_bytes(16, 1024, 16, 65536)
-    assert a == b and a < 5 * 2**30
+    assert a == b and a < 10 * 2**30
     assert lib.aussm_b200_scan_unitary_bwd_workspace_bytes(16, 1024, 16, 16384) == 16 * 1024 * 81 * 4
     assert lib.aussm_b200_set_option(b"no_such_option", 1) != 0
     assert b"unknown option" in lib.aussm_b200_last_error()
