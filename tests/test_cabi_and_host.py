@@ -70,3 +70,17 @@ def test_meta_kernels():
             u, u, torch.empty(3, 4, 3), torch.empty(3, 4), *[torch.empty(4)] * 4, torch.empty(3), u,
             torch.empty(2, 3, 4), torch.empty(2, 3, 4))
     assert outs[0].shape == (2, 3, 32) and outs[1].shape == (2, 3, 4) and outs[2].shape == (2, 3, 4)
+
+
+def test_bind_process_to_gpu_cpus_never_raises_and_keeps_the_affinity_without_a_gpu():
+    import os
+
+    import aussm_b200
+    before = os.sched_getaffinity(0)
+    n = aussm_b200.bind_process_to_gpu_cpus("cuda:0")
+    try:
+        assert isinstance(n, int) and n >= 0
+        if n == 0:
+            assert os.sched_getaffinity(0) == before
+    finally:
+        os.sched_setaffinity(0, before)
