@@ -24,11 +24,15 @@ def selective_scan_ref(u, delta, A, B, C, D=None, z=None, delta_bias=None, delta
     if delta_softplus:
         dlt = F.softplus(dlt)
     h = u.new_zeros(b, d, n)
+    # per-step views through unbind: one autograd node per tensor instead of one full-size gradient per step
+    dl_t = dlt.unsqueeze(-1).unbind(2)                        # (b, d, 1) each
+    du_t = (dlt * u).unsqueeze(-1).unbind(2)
+    B_t, C_t = B.unsqueeze(1).unbind(-1), C.unsqueeze(1).unbind(-1)      # (b, 1, n) each
     ys = []
     for t in range(l):
-        a = torch.exp(dlt[:, :, t, None] * A[None])                       # (b, d, n)
-        h = a * h + (dlt[:, :, t] * u[:, :, t])[..., None] * B[:, None, :, t]
-        ys.append((h * C[:, None, :, t]).sum(-1))
+        a = torch.exp(dl_t[t] * A[None])                                  # (b, d, n)
+        h = a * h + du_t[t] * B_t[t]
+        ys.append((h * C_t[t]).sum(-1))
     y = torch.stack(ys, dim=-1)
     if D is not None:
         y = y + u * D[None, :, None]

@@ -86,11 +86,12 @@ def scan_unitary_recurrence(theta, u, dt, z, B_r, B_theta, C_r, C_theta, D, h0_r
     bim = (B_r * torch.sin(B_theta)).reshape(1, 1, n)
     cre = (C_r * torch.cos(C_theta)).reshape(1, 1, n)
     cim = (C_r * torch.sin(C_theta)).reshape(1, 1, n)
-    cs, sn = torch.cos(theta), torch.sin(theta)
+    # per-step views through unbind: one autograd node per tensor instead of one full-size gradient per step
+    cs, sn = torch.cos(theta).unbind(-1), torch.sin(theta).unbind(-1)
+    drv = drive.unsqueeze(-1).unbind(2)
     out = []
     for t in range(l):
-        c, s = cs[..., t], sn[..., t]
-        s_t = drive[:, :, t, None]
+        c, s, s_t = cs[t], sn[t], drv[t]
         hr, hi = c * hr - s * hi + bre * s_t, s * hr + c * hi + bim * s_t
         out.append((cre * hr - cim * hi).sum(-1))
     proj = torch.stack(out, dim=-1)

@@ -21,11 +21,14 @@ def scan_complex_ref(rho, theta, u, dt, z, B, C, D):
     v = F.silu(u)
     drive = dt * v
     h = torch.zeros(b, d, n, dtype=cdt)
-    Bc, Cc = B.to(cdt), C.to(cdt)
+    # per-step views through unbind: one autograd node per tensor instead of one full-size gradient per step
+    lam_t = lam.unbind(-1)
+    drv_t = drive.unsqueeze(-1).unbind(2)                     # (b, d, 1) each
+    B_t, C_t = B.to(cdt).unsqueeze(1).unbind(-1), C.to(cdt).unsqueeze(1).unbind(-1)   # (b, 1, n) each
     ys = []
     for t in range(l):
-        h = lam[..., t] * h + drive[:, :, t, None] * Bc[:, None, :, t]
-        ys.append((h * Cc[:, None, :, t]).sum(-1).real)
+        h = lam_t[t] * h + drv_t[t] * B_t[t]
+        ys.append((h * C_t[t]).sum(-1).real)
     y = torch.stack(ys, dim=-1)
     return (y + v * D[None, :, None]) * F.silu(z)
 

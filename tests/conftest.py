@@ -24,3 +24,23 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter, exitstatus, config):
+    """Which branch of the parity rule every comparison passed by (tests/helpers.py::assert_parity)."""
+    from tests import helpers
+    log = helpers.PARITY_LOG
+    if not log:
+        return
+    tr = terminalreporter
+    counts = {}
+    for _test, _name, branch, _fo, _mx, _note in log:
+        counts[branch] = counts.get(branch, 0) + 1
+    tr.write_sep("-", "parity branches")
+    tr.write_line("comparisons: " + ", ".join(f"{k}: {v}" for k, v in sorted(counts.items())))
+    for test, name, branch, fo, mx, note in log:
+        if branch != "strict":
+            tr.write_line(f"  {branch:15s} {test} [{name}] outside {fo:.4%} max|err| {mx:.3e} {note}")
+    for test, name, branch, fo, mx, note in log:
+        if branch == "strict" and "baseline" in test:
+            tr.write_line(f"  {branch:15s} {test} [{name}] max|err| {mx:.3e}")

@@ -83,25 +83,43 @@ def parity_report(name, got, truth, ref32=None, atol=1e-5, rtol=1e-4):
     return fo, mx
 
 
+# every assert_parity call of the session: (test id, tensor, branch, fraction outside, max error, note);
+# tests/conftest.py prints a summary of it at the end of the run
+PARITY_LOG = []
+
+
+def _record(name, branch, fo, mx, note=""):
+    test = os.environ.get("PYTEST_CURRENT_TEST", "").split(" ")[0]
+    PARITY_LOG.append((test, name, branch, fo, mx, note))
+    print(f"    parity[{name}]: {branch} {note}")
+    return branch
+
+
 def assert_parity(name, got, truth, ref32=None, atol=1e-5, rtol=1e-4, scaled_tol=None):
     """Parity rule of this suite.
 
     Pass if every element is within ``atol + rtol*|truth|`` of the float64
-    truth.  Float32 arithmetic cannot guarantee that for long sequences (the
-    reference's own float32 oracle does not meet it either), so otherwise the
-    result must be at least as close to the truth as the float32 oracle is
-    (fraction of elements outside the tolerance, and largest error), or - when
-    no float32 oracle result is at hand - within ``scaled_tol`` of the truth
-    relative to the largest magnitude of the tensor.
+    truth ("strict").  Float32 arithmetic cannot guarantee that for long
+    sequences (the reference's own float32 oracle does not meet it either), so
+    otherwise the result must be at least as close to the truth as the float32
+    oracle is: no larger a fraction of elements outside the tolerance, and a
+    largest error of at most twice the oracle's ("no worse than the float32
+    oracle"); or - when no float32 oracle result is at hand - within
+    ``scaled_tol`` of the truth relative to the largest magnitude of the tensor
+    ("scaled").  The branch that let the case pass is printed and returned, so
+    that a test log shows it per tensor.
     """
     fo, mx = parity_report(name, got, truth, ref32, atol, rtol)
     if fo == 0.0:
-        return
+        return _record(name, "strict", fo, mx)
     if ref32 is not None:
         fo32, mx32 = outside_fraction(ref32, truth, atol, rtol)
-        assert fo <= max(fo32, 1e-3), f"{name}: {fo:.4%} of elements outside tolerance, float32 oracle {fo32:.4%}"
+        # a float32 oracle with nothing outside leaves no room: only the strict branch passes then
+        bound = 0.0 if fo32 == 0.0 else max(fo32, 1e-3)
+        assert fo <= bound, f"{name}: {fo:.4%} of elements outside tolerance, float32 oracle {fo32:.4%}"
         assert mx <= max(2.0 * mx32, atol), f"{name}: max error {mx:.3e} vs float32 oracle {mx32:.3e}"
-        return
+        return _record(name, "float32-oracle", fo, mx, f"oracle32 outside {fo32:.4%} max|err| {mx32:.3e}")
     assert scaled_tol is not None, f"{name}: {fo:.4%} of elements outside atol={atol} rtol={rtol}"
     se = scaled_error(got, truth)
     assert se <= scaled_tol, f"{name}: scaled error {se:.3e} > {scaled_tol:.1e}"
+    return _record(name, "scaled", fo, mx, f"scaled error {se:.3e} <= {scaled_tol:.1e}")
