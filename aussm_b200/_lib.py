@@ -25,8 +25,9 @@ SIGNATURES = {
     "aussm_b200_scan_unitary_bwd_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_scan_unitary_bwd": (_I, [_P] * 25 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_scan_unitary_bwd_static": (_I, [_P] * 25 + [_I] * 4 + [_P]),
-    "aussm_b200_gemm_tf32x3_workspace_bytes": (_Z, [_I] * 6),
-    "aussm_b200_gemm_tf32x3": (_I, [_P, _I, _I, _P, _I, _I, _P] + [_I] * 6 + [_P, _Z, _P]),
+    "aussm_b200_kernel_launches": (ctypes.c_ulonglong, []),
+    "aussm_b200_gemm_split3_workspace_bytes": (_Z, [_I] * 8),
+    "aussm_b200_gemm_split3": (_I, [_P, _I, _I, _P, _I, _I, _P] + [_I] * 6 + [_P, _Z, _P]),
     "aussm_b200_unitary_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_scan_complex_ckpt_floats": (_Z, [_I] * 4),
     "aussm_b200_scan_complex_bwd_workspace_bytes": (_Z, [_I] * 4),

@@ -12,8 +12,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaussm_b200.so")
-SOURCES = ["scan_unitary.cu", "projection.cu", "gemm_tf32x3.cu", "scan_s6.cu", "scan_complex.cu", "api.cu", "api_s6.cu", "api_complex.cu", "noalloc.cu"]
-HEADERS = ["common.cuh", "scan_unitary.cuh", "projection.cuh", "gemm_tf32x3.cuh", "scan_s6.cuh", "scan_complex.cuh", os.path.join("..", "..", "include", "aussm_b200.h")]
+SOURCES = ["scan_unitary.cu", "projection.cu", "gemm_split3.cu", "scan_s6.cu", "scan_complex.cu", "api.cu", "api_s6.cu", "api_complex.cu", "noalloc.cu"]
+HEADERS = ["common.cuh", "scan_unitary.cuh", "projection.cuh", "gemm_split3.cuh", "host_common.cuh", "scan_s6.cuh", "scan_complex.cuh", os.path.join("..", "..", "include", "aussm_b200.h")]
 
 
 def _nvcc() -> str:
@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if p.returncode:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
     cuda_lib = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "lib64")
-    link = [_nvcc(), "-shared", "-o", LIB, *objs, "-L", cuda_lib, "-lcublas", "-lcudart",
+    link = [_nvcc(), "-shared", "-o", LIB, *objs, "-L", cuda_lib, "-lcudart",
             "-Xlinker", "-rpath=" + cuda_lib]
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode:

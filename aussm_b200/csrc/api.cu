@@ -7,10 +7,13 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
+#include <mutex>
 #include <string>
+#include <unordered_map>
 
 #include "../../include/aussm_b200.h"
-#include "gemm_tf32x3.cuh"
+#include "gemm_split3.cuh"
 #include "projection.cuh"
 #include "scan_unitary.cuh"
 
@@ -18,8 +21,13 @@ namespace aussm {
 
 namespace {
 thread_local std::string t_last_error;
-int g_window_override = 0;   // option "gemm_tile": steps per window of the drop-in pipeline (0 = automatic)
+thread_local int t_window_steps = 0;   // option "window_steps" of the calling thread (0 = automatic)
+std::atomic<unsigned long long> g_launches{0};
 }  // namespace
+
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+int window_steps_option() { return t_window_steps; }
 
 void set_error(const char* fmt, ...) {
     char buf[512];
@@ -63,13 +71,13 @@ struct Plan {
     size_t off_theta, off_h, off_gh, off_part, off_proj, total;   // byte offsets
 };
 
-Plan make_plan(int B, int D, int N, int L) {
+Plan make_plan(int B, int D, int N, int L, int window_steps = window_steps_option()) {
     Plan p;
     p.rows = (long long)B * D * N;
-    const long long Lp = ((long long)L + 3) / 4 * 4;
+    const long long Lp = ((long long)L + 7) / 8 * 8;
     long long w;
-    if (g_window_override > 0) {
-        w = ((long long)g_window_override + 63) / 64 * 64;
+    if (window_steps > 0) {
+        w = ((long long)window_steps + 63) / 64 * 64;
     } else {
         // about 2 GiB of phases per window, at least 64 and at most 16384 steps (longer windows: fewer, better
         // filled launches; measured 138 -> 132 ms on the end-to-end benchmark step against 4096-step windows)
@@ -88,15 +96,47 @@ Plan make_plan(int B, int D, int N, int L) {
     off = align_up(off + (size_t)p.rows * 2 * 4, 256);
     p.off_part = off;
     off = align_up(off + scan_bwd_partial_floats((long long)B * D, N) * 4, 256);
-    p.off_proj = off;    // TF32 hi/lo parts of x, of the u window and of the dtheta window
-    off = align_up(off + proj_scratch_floats(B, D, N, p.ldw) * 4, 256);
+    p.off_proj = off;    // FP16 hi/lo parts of x, of the u window and of the dtheta window
+    off = align_up(off + proj_scratch_bytes(B, D, N, p.ldw), 256);
     p.total = off;
     return p;
 }
 
+// The layout of a kept-phase buffer (window length and row pitch) follows from the plan of the forward call,
+// which depends on the calling thread's "window_steps" option.  The forward call notes the layout it used under
+// the buffer's address (host side, no device traffic); the backward call refuses a buffer that it finds noted
+// with another layout, so a changed option between the two calls is an error instead of wrong gradients.
+struct KeepLayout {
+    int window;
+    long long ldw, rows;
+};
+std::mutex g_keep_mutex;
+std::unordered_map<const void*, KeepLayout> g_keep_layouts;
+
 size_t keep_bytes_of(const Plan& pl, int L) {
     const size_t nwin = (size_t)((L + pl.window - 1) / pl.window);
     return align_up(nwin * (size_t)pl.rows * pl.ldw * sizeof(float), 256);
+}
+
+void keep_note_layout(const void* keep, const Plan& pl) {
+    std::lock_guard<std::mutex> lock(g_keep_mutex);
+    g_keep_layouts[keep] = KeepLayout{pl.window, pl.ldw, pl.rows};
+}
+
+// consumes the note (the backward call overwrites the phases: a buffer serves one backward call)
+int keep_check_layout(const void* keep, const Plan& pl) {
+    std::lock_guard<std::mutex> lock(g_keep_mutex);
+    auto it = g_keep_layouts.find(keep);
+    if (it == g_keep_layouts.end()) return AUSSM_OK;        // written by another process image or already consumed
+    const KeepLayout k = it->second;
+    g_keep_layouts.erase(it);
+    if (k.window != pl.window || k.ldw != pl.ldw || k.rows != pl.rows) {
+        set_error("unitary_bwd_kept: the phase buffer was written with another layout (window %d, pitch %lld) than "
+                  "this call uses (window %d, pitch %lld): the window_steps option changed between forward and "
+                  "backward", k.window, k.ldw, pl.window, pl.ldw);
+        return AUSSM_EINVAL;
+    }
+    return AUSSM_OK;
 }
 
 bool keep_ok(const char* who, const void* keep, size_t keep_bytes, const Plan& pl, int L) {
@@ -130,7 +170,7 @@ int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, flo
         const int tl = (int)std::min<long long>(pl.window, a.L - t0);
         const ProjDims pd = {a.B, a.D, a.N, a.L, pl.ldw, t0, tl};
         if (keep) theta_w = keep + (size_t)w * pl.rows * pl.ldw;
-        if (int rc = proj_theta(pd, a.x, a.u, theta_w, ps, stream)) return rc;
+        if (int rc = proj_theta(pd, a.u, theta_w, ps, stream)) return rc;
         const bool last = (w == nwin - 1);
         ScanFwdParams sp = {};
         sp.theta = theta_w;
@@ -172,22 +212,16 @@ int aussm_b200_device_status(aussm_stream_t stream) {
     return v;
 }
 
+unsigned long long aussm_b200_kernel_launches(void) { return launch_count(); }
+
 int aussm_b200_set_option(const char* name, int value) {
     if (!name) return AUSSM_EINVAL;
-    ScanOptions& o = scan_options();
-    if (!strcmp(name, "fast_trig")) o.fast_trig = value;
-    else if (!strcmp(name, "force_plain")) o.force_plain = value;
-    else if (!strcmp(name, "variant")) o.variant = value;
-    else if (!strcmp(name, "blocks_per_sm")) o.blocks_per_sm = value;
-    else if (!strcmp(name, "gemm_tile")) g_window_override = value;
-    else if (!strcmp(name, "gemm_backend")) set_gemm_backend(value);
-    else if (!strcmp(name, "gemm_pair")) set_gemm_pair(value);
-    else if (!strcmp(name, "gemm_probe")) set_gemm_probe(value);
-    else {
-        set_error("unknown option '%s'", name);
-        return AUSSM_EINVAL;
+    if (!strcmp(name, "window_steps")) {
+        t_window_steps = value > 0 ? value : 0;
+        return AUSSM_OK;
     }
-    return AUSSM_OK;
+    set_error("unknown option '%s'", name);
+    return AUSSM_EINVAL;
 }
 
 int aussm_b200_scan_unitary_fwd(const float* theta, const float* u, const float* dt, const float* z,
@@ -265,55 +299,60 @@ int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const 
     return AUSSM_OK;
 }
 
-size_t aussm_b200_gemm_tf32x3_workspace_bytes(int M, int N, int K, int batches, int a_batched, int b_batched) {
+// packed operands: K-major = (rows, K) with K contiguous; MN-major = (K, rows) with rows contiguous
+namespace {
+struct PackedDims { long long rows, cols, pitch; };
+PackedDims packed_dims(int mn_major, int rows_mn, int K) {
+    PackedDims p;
+    p.rows = mn_major ? K : rows_mn;
+    p.cols = mn_major ? rows_mn : K;
+    p.pitch = (p.cols + 7) / 8 * 8;         // halves: rows of the FP16 parts start 16-byte aligned
+    return p;
+}
+}  // namespace
+
+size_t aussm_b200_gemm_split3_workspace_bytes(int M, int N, int K, int batches, int a_mn_major, int a_batched,
+                                              int b_mn_major, int b_batched) {
     if (M <= 0 || N <= 0 || K <= 0 || batches <= 0) return 0;
-    const size_t na = (size_t)M * K * (a_batched ? batches : 1), nb = (size_t)N * K * (b_batched ? batches : 1);
-    return align_up(2 * (na + nb) * sizeof(float) + 1024, 256);
+    const PackedDims a = packed_dims(a_mn_major, M, K), b = packed_dims(b_mn_major, N, K);
+    const size_t na = align_up((size_t)a.rows * a.pitch * (a_batched ? batches : 1), 128);
+    const size_t nb = align_up((size_t)b.rows * b.pitch * (b_batched ? batches : 1), 128);
+    return 2 * (na + nb) * 2 + 1024;
 }
 
-int aussm_b200_gemm_tf32x3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
+int aussm_b200_gemm_split3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
                            int b_batched, float* C, int M, int N, int K, int batches, int reduce_batches, int beta,
                            void* workspace, size_t workspace_bytes, aussm_stream_t stream_) {
     if (!A || !Bm || !C || M <= 0 || N <= 0 || K <= 0 || batches <= 0) {
-        set_error("gemm_tf32x3: null pointer or non-positive size");
+        set_error("gemm_split3: null pointer or non-positive size");
         return AUSSM_EINVAL;
     }
-    const size_t need = aussm_b200_gemm_tf32x3_workspace_bytes(M, N, K, batches, a_batched, b_batched);
+    const size_t need = aussm_b200_gemm_split3_workspace_bytes(M, N, K, batches, a_mn_major, a_batched, b_mn_major,
+                                                               b_batched);
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) {
-        set_error("gemm_tf32x3: workspace of %zu bytes (256-byte aligned) required, got %zu", need, workspace_bytes);
+        set_error("gemm_split3: workspace of %zu bytes (256-byte aligned) required, got %zu", need, workspace_bytes);
         return AUSSM_EWORKSPACE;
     }
     cudaStream_t stream = (cudaStream_t)stream_;
-    // packed operands: K-major = (rows, K) with K contiguous; MN-major = (K, rows) with rows contiguous
-    const long long a_rows = a_mn_major ? K : M, a_cols = a_mn_major ? M : K;
-    const long long b_rows = b_mn_major ? K : N, b_cols = b_mn_major ? N : K;
+    const PackedDims a = packed_dims(a_mn_major, M, K), b = packed_dims(b_mn_major, N, K);
     const int na = a_batched ? batches : 1, nb = b_batched ? batches : 1;
-    float* a_hi = static_cast<float*>(workspace);
-    float* a_lo = a_hi + (size_t)a_rows * a_cols * na;
-    float* b_hi = a_lo + (size_t)a_rows * a_cols * na;
-    float* b_lo = b_hi + (size_t)b_rows * b_cols * nb;
-    // FP16 parts (half the bytes, twice the tensor-core rate) when every pitch is a multiple of 8, else TF32 parts
-    const bool half = gemm_backend() == 0 && a_cols % 8 == 0 && b_cols % 8 == 0;
-    unsigned* amax = reinterpret_cast<unsigned*>(b_lo + (size_t)b_rows * b_cols * nb);   // in the spare 1 KiB
-    if (half) {
-        if (int rc = split_f16(A, a_cols, a_rows * a_cols, a_hi, a_lo, a_cols, a_rows * a_cols, a_rows, a_cols, na,
-                               amax + 0, stream))
-            return rc;
-        if (int rc = split_f16(Bm, b_cols, b_rows * b_cols, b_hi, b_lo, b_cols, b_rows * b_cols, b_rows, b_cols, nb,
-                               amax + 1, stream))
-            return rc;
-    } else {
-        if (int rc = split_tf32(A, a_cols, a_rows * a_cols, a_hi, a_lo, a_cols, a_rows * a_cols, a_rows, a_cols, na,
-                                stream))
-            return rc;
-        if (int rc = split_tf32(Bm, b_cols, b_rows * b_cols, b_hi, b_lo, b_cols, b_rows * b_cols, b_rows, b_cols, nb,
-                                stream))
-            return rc;
-    }
-    const SplitOperand sa = {a_hi, a_lo, a_mn_major, a_cols, a_batched ? a_rows * a_cols : 0, half ? amax + 0 : nullptr};
-    const SplitOperand sb = {b_hi, b_lo, b_mn_major, b_cols, b_batched ? b_rows * b_cols : 0, half ? amax + 1 : nullptr};
+    const size_t a_halves = align_up((size_t)a.rows * a.pitch * na, 128), b_halves = align_up((size_t)b.rows * b.pitch * nb, 128);
+    char* w = static_cast<char*>(workspace);
+    void* a_hi = w;
+    void* a_lo = w + a_halves * 2;
+    void* b_hi = w + a_halves * 4;
+    void* b_lo = w + a_halves * 4 + b_halves * 2;
+    unsigned* amax = reinterpret_cast<unsigned*>(w + a_halves * 4 + b_halves * 4);   // in the spare 1 KiB
+    if (int rc = split_f16(A, a.cols, a.rows * a.cols, a_hi, a_lo, a.pitch, a.rows * a.pitch, a.rows, a.cols, na,
+                           amax + 0, stream))
+        return rc;
+    if (int rc = split_f16(Bm, b.cols, b.rows * b.cols, b_hi, b_lo, b.pitch, b.rows * b.pitch, b.rows, b.cols, nb,
+                           amax + 1, stream))
+        return rc;
+    const SplitOperand sa = {a_hi, a_lo, a_mn_major, a.pitch, a_batched ? a.rows * a.pitch : 0, amax + 0};
+    const SplitOperand sb = {b_hi, b_lo, b_mn_major, b.pitch, b_batched ? b.rows * b.pitch : 0, amax + 1};
     const GemmShape shape = {M, N, K, batches, reduce_batches, beta, N, reduce_batches ? 0 : (long long)M * N};
-    return gemm_tf32x3(sa, sb, C, shape, stream);
+    return gemm_split3(sa, sb, C, shape, stream);
 }
 
 size_t aussm_b200_unitary_workspace_bytes(int B, int D, int N, int L) {
@@ -325,7 +364,7 @@ static int unitary_fwd_impl(const float* u, const float* dt, const float* x, con
                             const float* B_theta, const float* C_r, const float* C_theta, const float* Dskip,
                             const float* z, const float* h0_re, const float* h0_im, float* y, float* h1_re,
                             float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
-                            aussm_stream_t stream, float* keep, size_t keep_bytes) {
+                            aussm_stream_t stream, void* keep, size_t keep_bytes) {
     if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
     if (!u || !dt || !x || !x_bias || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !z || !y) {
         set_error("unitary_fwd: null input or output pointer");
@@ -346,10 +385,11 @@ static int unitary_fwd_impl(const float* u, const float* dt, const float* x, con
     float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
     const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
     ProjScratch ps;
-    proj_scratch_bind(ps, reinterpret_cast<float*>(ws + pl.off_proj), B, D, N, pl.ldw);
-    if (int rc = proj_begin(B, D, N, L, pl.ldw, x, u, ps, (cudaStream_t)stream)) return rc;
+    proj_scratch_bind(ps, ws + pl.off_proj, B, D, N, pl.ldw);
+    if (int rc = proj_begin(B, D, N, x, ps, (cudaStream_t)stream)) return rc;
+    if (keep) keep_note_layout(keep, pl);
     return run_unitary_fwd(a, h0_re, h0_im, y, h1_re ? h1_re : cur_re, h1_im ? h1_im : cur_re + pl.rows, ws, pl, ps,
-                           (cudaStream_t)stream, keep);
+                           (cudaStream_t)stream, static_cast<float*>(keep));
 }
 
 int aussm_b200_unitary_fwd(const float* u, const float* dt, const float* x, const float* x_bias, const float* B_r,
@@ -376,7 +416,7 @@ int aussm_b200_unitary_fwd_keep(const float* u, const float* dt, const float* x,
         return AUSSM_EINVAL;
     }
     return unitary_fwd_impl(u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, h0_re, h0_im, y, h1_re, h1_im, B,
-                            D, N, L, workspace, workspace_bytes, stream, static_cast<float*>(theta_keep), keep_bytes);
+                            D, N, L, workspace, workspace_bytes, stream, theta_keep, keep_bytes);
 }
 
 static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* u,
@@ -386,7 +426,7 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
                             const float* h1_im, float* du, float* ddt, float* dx, float* dx_bias, float* dB_r,
                             float* dB_theta, float* dC_r, float* dC_theta, float* dD, float* dz, float* dh0_re,
                             float* dh0_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
-                            aussm_stream_t stream_, float* keep, size_t keep_bytes) {
+                            aussm_stream_t stream_, void* keep_buf, size_t keep_bytes) {
     if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
     if (!grad_y || !u || !dt || !x || !x_bias || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !z || !du ||
         !ddt || !dx || !dx_bias || !dB_r || !dB_theta || !dC_r || !dC_theta || !dD || !dz) {
@@ -404,7 +444,8 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
                   workspace_bytes);
         return AUSSM_EWORKSPACE;
     }
-    if (!keep_ok("unitary_bwd_kept", keep, keep_bytes, pl, L)) return AUSSM_EWORKSPACE;
+    if (!keep_ok("unitary_bwd_kept", keep_buf, keep_bytes, pl, L)) return AUSSM_EWORKSPACE;
+    float* keep = static_cast<float*>(keep_buf);
     if (keep && !h1_re) {
         set_error("unitary_bwd_kept: the final state of the forward call is required with kept phases");
         return AUSSM_EINVAL;
@@ -421,9 +462,12 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
     float* part_d = part_bc + nch * N * 4;
     float* part_rowsum = part_d + nch;
     const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
+    if (keep_buf) {
+        if (int rc = keep_check_layout(keep_buf, pl)) return rc;
+    }
     ProjScratch ps;
-    proj_scratch_bind(ps, reinterpret_cast<float*>(ws + pl.off_proj), B, D, N, pl.ldw);
-    if (int rc = proj_begin(B, D, N, L, pl.ldw, x, u, ps, stream)) return rc;
+    proj_scratch_bind(ps, ws + pl.off_proj, B, D, N, pl.ldw);
+    if (int rc = proj_begin(B, D, N, x, ps, stream)) return rc;
 
     // final state: given by the caller, or recomputed by a state-only forward sweep
     const float* hend_re = h1_re;
@@ -444,7 +488,7 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
         if (keep) {
             theta_w = keep + (size_t)w * pl.rows * pl.ldw;    // phases of the forward call; dtheta replaces them
             if (int rc = proj_split_u(pd, u, ps, stream)) return rc;
-        } else if (int rc = proj_theta(pd, x, u, theta_w, ps, stream)) {
+        } else if (int rc = proj_theta(pd, u, theta_w, ps, stream)) {
             return rc;
         }
         ScanBwdParams p = {};
@@ -466,15 +510,12 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
         p.nch = (int)nch; p.Dmod = D; p.N = N; p.L = tl;
         p.ld_theta = pl.ldw; p.ld_dtheta = pl.ldw; p.ld_row = L;
         // the scan leaves max|dtheta| of the window behind for the FP16 split of the adjoint GEMMs
-        const bool fused_amax = ps.use_tensor_cores && ps.half;
-        if (fused_amax) {
-            cudaError_t em = cudaMemsetAsync(ps.amax + 2, 0, sizeof(unsigned), stream);
-            if (em != cudaSuccess) return cuda_fail(em, "clearing the dtheta maximum");
-            p.dtheta_amax = ps.amax + 2;
-        }
+        cudaError_t em = cudaMemsetAsync(ps.amax + 2, 0, sizeof(unsigned), stream);
+        if (em != cudaSuccess) return cuda_fail(em, "clearing the dtheta maximum");
+        p.dtheta_amax = ps.amax + 2;
         cudaError_t e = launch_scan_unitary_bwd(p, stream);
         if (e != cudaSuccess) return cuda_fail(e, "unitary scan backward launch");
-        if (int rc = proj_adjoints(pd, theta_w, x, u, dx, du, first, ps, stream, fused_amax)) return rc;
+        if (int rc = proj_adjoints(pd, theta_w, dx, du, first, ps, stream, true)) return rc;
     }
     ReduceParams r = {};
     r.part_bc = part_bc; r.part_d = part_d; r.part_rowsum = part_rowsum;
@@ -513,8 +554,7 @@ int aussm_b200_unitary_bwd_kept(const float* grad_y, const float* gh1_re, const 
     }
     return unitary_bwd_impl(grad_y, gh1_re, gh1_im, u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, h0_re,
                             h0_im, h1_re, h1_im, du, ddt, dx, dx_bias, dB_r, dB_theta, dC_r, dC_theta, dD, dz, dh0_re,
-                            dh0_im, B, D, N, L, workspace, workspace_bytes, stream, static_cast<float*>(theta_keep),
-                            keep_bytes);
+                            dh0_im, B, D, N, L, workspace, workspace_bytes, stream, theta_keep, keep_bytes);
 }
 
 }  // extern "C"

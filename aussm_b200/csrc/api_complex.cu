@@ -3,7 +3,7 @@
 #include <stdint.h>
 
 #include "../../include/aussm_b200.h"
-#include "projection.cuh"     // set_error
+#include "host_common.cuh"
 #include "scan_complex.cuh"
 
 using namespace aussm;

@@ -194,29 +194,13 @@ __device__ __forceinline__ void sincos2_accurate(float2 theta, float2& sn, float
     cs = make_float2(__int_as_float(__float_as_int(c.x) ^ sx), __int_as_float(__float_as_int(c.y) ^ sy));
 }
 
-// Special-function-unit variant (2^-21.4 absolute on [-pi, pi]); kept for
-// measurement, selected at compile time by the kernels' FAST parameter.
-__device__ __forceinline__ void sincos_fast(float theta, float& sn, float& cs) {
-    float k = rintf(theta * 0.15915494309189535f);
-    float r = fmaf(k, -6.2831854820251465f, theta);
-    r = fmaf(k, 1.7484555314695172e-07f, r);
-    sn = __sinf(r);
-    cs = __cosf(r);
-}
-
 // four angles -> four (sin, cos) pairs
-template <bool FAST>
 __device__ __forceinline__ void sincos4(const float (&th)[4], float (&sn)[4], float (&cs)[4]) {
-    if (FAST) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) sincos_fast(th[e], sn[e], cs[e]);
-    } else {
-        float2 s01, c01, s23, c23;
-        sincos2_accurate(make_float2(th[0], th[1]), s01, c01);
-        sincos2_accurate(make_float2(th[2], th[3]), s23, c23);
-        sn[0] = s01.x; sn[1] = s01.y; sn[2] = s23.x; sn[3] = s23.y;
-        cs[0] = c01.x; cs[1] = c01.y; cs[2] = c23.x; cs[3] = c23.y;
-    }
+    float2 s01, c01, s23, c23;
+    sincos2_accurate(make_float2(th[0], th[1]), s01, c01);
+    sincos2_accurate(make_float2(th[2], th[3]), s23, c23);
+    sn[0] = s01.x; sn[1] = s01.y; sn[2] = s23.x; sn[3] = s23.y;
+    cs[0] = c01.x; cs[1] = c01.y; cs[2] = c23.x; cs[3] = c23.y;
 }
 
 // ---------------------------------------------------------------------------

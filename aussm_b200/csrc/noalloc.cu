@@ -10,22 +10,25 @@
 // allocator's lock, a plug-in host that hands out only the input and output
 // buffers), or a runtime with a fixed memory plan that has no spare buffer to
 // lend.  For them the scratch lives in a file-scope device array that is part
-// of the library image: it exists as soon as the library is loaded on a GPU and
-// is never freed, so the call itself performs no cudaMalloc, no cudaFree and no
-// allocating library routine.
+// of the library's device code and is never freed, so the call itself performs
+// no cudaMalloc, no cudaFree and no allocating library routine.  The runtime
+// loads device code lazily: the first call on a device makes it load this
+// module (the array comes into being then, which may reserve memory and
+// synchronise the device), so callers make one warm-up call per device before
+// the region where that is off limits.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include <mutex>
 
 #include "../../include/aussm_b200.h"
-#include "projection.cuh"     // set_error
+#include "host_common.cuh"
 #include "scan_unitary.cuh"
 
 namespace aussm {
 namespace {
 
-// 4 MiB per GPU that loads the library, held until the process exits.
+// 4 MiB per GPU on which the entry point has run (or that loaded the library eagerly), held until the process exits.
 constexpr size_t kStaticScratchFloats = (size_t)AUSSM_STATIC_SCRATCH_BYTES / sizeof(float);
 static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
@@ -39,9 +42,14 @@ std::mutex g_scratch_mutex;
 int static_scratch_address(float** out) {
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    if (e != cudaSuccess) {
         set_error("scan_unitary_bwd_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
         return AUSSM_ECUDA;
+    }
+    if (dev < 0 || dev >= kMaxDevices) {
+        set_error("scan_unitary_bwd_static: device ordinal %d is outside the %d devices this entry point keeps an "
+                  "address for", dev, kMaxDevices);
+        return AUSSM_EINVAL;
     }
     std::lock_guard<std::mutex> lock(g_scratch_mutex);
     if (!g_scratch_addr[dev]) {

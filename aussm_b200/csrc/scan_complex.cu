@@ -16,6 +16,7 @@
 #include <stdint.h>
 
 #include "common.cuh"
+#include "host_common.cuh"
 
 namespace aussm {
 namespace {
@@ -127,7 +128,7 @@ __device__ __forceinline__ void lambda4(const float4 r4, const float4 t4, float 
     const float tv[4] = {t4.x, t4.y, t4.z, t4.w};
     const float rv[4] = {r4.x, r4.y, r4.z, r4.w};
     float sn[4], cs[4];
-    sincos4<false>(tv, sn, cs);
+    sincos4(tv, sn, cs);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         const float m = exp2f(rv[e] * kLog2e);
@@ -523,6 +524,7 @@ cudaError_t launch_nl(Kern kern, const Params& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     const long long blocks = (long long)(p.nch / p.Dmod) * ((p.Dmod + C::CPW - 1) / C::CPW);
     kern<<<(unsigned)blocks, 32, C::SMEM_BYTES, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -548,6 +550,7 @@ cudaError_t launch_cplx_bwd(const CplxBwdParams& p, cudaStream_t stream) {
 
 cudaError_t launch_cplx_reduce_D(const float* part_D, float* dD, int batch, int D, cudaStream_t stream) {
     cplx_reduce_D_kernel<<<(D + 255) / 256, 256, 0, stream>>>(part_D, dD, batch, D);
+    count_launch();
     return cudaGetLastError();
 }
 

@@ -21,6 +21,7 @@
 #include <stdint.h>
 
 #include "common.cuh"
+#include "host_common.cuh"
 
 namespace aussm {
 namespace {
@@ -487,6 +488,7 @@ cudaError_t launch_fwd_nl(const S6FwdParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     const long long blocks = (long long)(p.nch / p.Dmod) * ((p.Dmod + C::CPW - 1) / C::CPW);
     kern<<<(unsigned)blocks, 32, C::SMEM_BYTES, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -498,6 +500,7 @@ cudaError_t launch_bwd_nl(const S6BwdParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     const long long blocks = (long long)(p.nch / p.Dmod) * ((p.Dmod + C::CPW - 1) / C::CPW);
     kern<<<(unsigned)blocks, 32, C::SMEM_BYTES, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 
@@ -524,6 +527,7 @@ cudaError_t launch_s6_bwd(const S6BwdParams& p, cudaStream_t stream) {
 cudaError_t launch_s6_reduce(const S6ReduceParams& p, cudaStream_t stream) {
     const long long total = (long long)p.D * p.N + p.D;
     s6_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 

@@ -46,11 +46,6 @@ namespace aussm {
 
 __device__ int g_device_status = 0;
 
-ScanOptions& scan_options() {
-    static ScanOptions o = {0, 0, 0, 0};
-    return o;
-}
-
 int* device_status_ptr() {
     int* ptr = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_device_status) != cudaSuccess) return nullptr;
@@ -258,7 +253,7 @@ __device__ __forceinline__ void plain_load_tile(float* stage, const float* theta
 // ---------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------
-template <class C, bool ASYNC, bool FAST, bool NORM, bool BIAS>
+template <class C, bool ASYNC, bool NORM, bool BIAS>
 __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, long long ch0, int nvalid, int lane,
                                          StateConsts (&sc)[C::SPT]) {
     constexpr int NL = C::NL, SPT = C::SPT, T = C::T, TP = C::TP, STAGES = C::STAGES, AUX = C::AUX, VW = C::VW;
@@ -349,7 +344,7 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
                     for (int e = 0; e < 4; ++e) tv[e] += sc[k].bias;
                 }
                 float sn[4], cs[4];
-                sincos4<FAST>(tv, sn, cs);
+                sincos4(tv, sn, cs);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     if (!ASYNC && 4 * q + e >= tlen) {           // ragged tail (plain path only)
@@ -433,7 +428,7 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
     }
 }
 
-template <class C, bool ASYNC, bool FAST, bool BIAS>
+template <class C, bool ASYNC, bool BIAS>
 __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const ScanFwdParams p) {
     extern __shared__ __align__(128) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -459,16 +454,16 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const S
             float a, b;
             normalise_consts(sc[k], a, b);
         }
-        fwd_warp<C, ASYNC, FAST, true, BIAS>(p, wsm, ch0, nvalid, lane, sc);
+        fwd_warp<C, ASYNC, true, BIAS>(p, wsm, ch0, nvalid, lane, sc);
     } else {
-        fwd_warp<C, ASYNC, FAST, false, BIAS>(p, wsm, ch0, nvalid, lane, sc);
+        fwd_warp<C, ASYNC, false, BIAS>(p, wsm, ch0, nvalid, lane, sc);
     }
 }
 
 // ---------------------------------------------------------------------------
 // Backward
 // ---------------------------------------------------------------------------
-template <class C, bool ASYNC, bool FAST, bool NORM, bool BIAS>
+template <class C, bool ASYNC, bool NORM, bool BIAS>
 __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, long long ch0, int nvalid, int lane,
                                          StateConsts (&sc)[C::SPT], const float (&ccr)[C::SPT],
                                          const float (&cci)[C::SPT]) {
@@ -603,7 +598,7 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
                         for (int e = 0; e < 4; ++e) tv[e] += sc[k].bias;
                     }
                     float sn[4], cs[4];
-                    sincos4<FAST>(tv, sn, cs);
+                    sincos4(tv, sn, cs);
                     float dth[4];
 #pragma unroll
                     for (int e = 3; e >= 0; --e) {
@@ -799,7 +794,7 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
     }
 }
 
-template <class C, bool ASYNC, bool FAST, bool BIAS>
+template <class C, bool ASYNC, bool BIAS>
 __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_bwd_kernel(const ScanBwdParams p) {
     extern __shared__ __align__(128) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -825,9 +820,9 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_bwd_kernel(const S
     if (__all_sync(0xffffffffu, ok)) {
 #pragma unroll
         for (int k = 0; k < C::SPT; ++k) normalise_consts(sc[k], ccr[k], cci[k]);
-        bwd_warp<C, ASYNC, FAST, true, BIAS>(p, wsm, ch0, nvalid, lane, sc, ccr, cci);
+        bwd_warp<C, ASYNC, true, BIAS>(p, wsm, ch0, nvalid, lane, sc, ccr, cci);
     } else {
-        bwd_warp<C, ASYNC, FAST, false, BIAS>(p, wsm, ch0, nvalid, lane, sc, ccr, cci);
+        bwd_warp<C, ASYNC, false, BIAS>(p, wsm, ch0, nvalid, lane, sc, ccr, cci);
     }
 }
 
@@ -887,59 +882,46 @@ __global__ void __launch_bounds__(256) reduce_param_grads_kernel(const ReducePar
 // ---------------------------------------------------------------------------
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// Dynamic shared memory to request: what the tile shape needs, or more when the caller wants to cap the
-// number of resident blocks per SM (228 KB per SM, 1 KB reserved per block) to fit the grid in whole waves.
-inline size_t padded_smem(size_t needed) {
-    const int want = scan_options().blocks_per_sm;
-    if (want <= 0) return needed;
-    const size_t per_block = (size_t)233472 / (size_t)want;
-    if (per_block <= 1024 + needed) return needed;
-    size_t padded = (per_block - 1024) / 128 * 128;
-    if (padded > 232448) padded = 232448;
-    return padded > needed ? padded : needed;
-}
-
-template <class C, bool ASYNC, bool FAST, bool BIAS>
+template <class C, bool ASYNC, bool BIAS>
 cudaError_t launch_fwd_cfg(const ScanFwdParams& p, cudaStream_t stream) {
-    auto kern = scan_unitary_fwd_kernel<C, ASYNC, FAST, BIAS>;
-    const size_t smem = padded_smem(C::SMEM_BYTES);
+    auto kern = scan_unitary_fwd_kernel<C, ASYNC, BIAS>;
+    const size_t smem = C::SMEM_BYTES;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const long long tasks = ((long long)p.nch + C::CPW - 1) / C::CPW;
     const long long blocks = (tasks + C::WARPS - 1) / C::WARPS;
     kern<<<(unsigned)blocks, C::WARPS * 32, smem, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 
-template <class C, bool ASYNC, bool FAST, bool BIAS>
+template <class C, bool ASYNC, bool BIAS>
 cudaError_t launch_bwd_cfg(const ScanBwdParams& p, cudaStream_t stream) {
-    auto kern = scan_unitary_bwd_kernel<C, ASYNC, FAST, BIAS>;
-    const size_t smem = padded_smem(C::SMEM_BYTES);
+    auto kern = scan_unitary_bwd_kernel<C, ASYNC, BIAS>;
+    const size_t smem = C::SMEM_BYTES;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const long long tasks = ((long long)p.nch + C::CPW - 1) / C::CPW;
     const long long blocks = (tasks + C::WARPS - 1) / C::WARPS;
     kern<<<(unsigned)blocks, C::WARPS * 32, smem, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 
-// Runtime switches -> template parameters.  The plain (unaligned) path and the
-// special-function trigonometry are fallback / measurement variants and are
-// instantiated with the phase offset always on, to keep the build small.
+// Runtime properties -> template parameters.  The plain (unaligned) path is instantiated with the phase
+// offset always on, to keep the build small.
 template <class C>
-cudaError_t launch_fwd_sel(const ScanFwdParams& p, bool async, bool fast, cudaStream_t s) {
+cudaError_t launch_fwd_sel(const ScanFwdParams& p, bool async, cudaStream_t s) {
     const bool bias = p.theta_bias != nullptr;
-    if (!async) return launch_fwd_cfg<C, false, false, true>(p, s);
-    if (fast) return launch_fwd_cfg<C, true, true, true>(p, s);
-    return bias ? launch_fwd_cfg<C, true, false, true>(p, s) : launch_fwd_cfg<C, true, false, false>(p, s);
+    if (!async) return launch_fwd_cfg<C, false, true>(p, s);
+    return bias ? launch_fwd_cfg<C, true, true>(p, s) : launch_fwd_cfg<C, true, false>(p, s);
 }
 
 template <class C>
-cudaError_t launch_bwd_sel(const ScanBwdParams& p, bool async, bool fast, cudaStream_t s) {
+cudaError_t launch_bwd_sel(const ScanBwdParams& p, bool async, cudaStream_t s) {
     const bool bias = p.theta_bias != nullptr || p.part_rowsum != nullptr;
-    if (!async) return launch_bwd_cfg<C, false, false, true>(p, s);
-    if (fast) return launch_bwd_cfg<C, true, true, true>(p, s);
-    return bias ? launch_bwd_cfg<C, true, false, true>(p, s) : launch_bwd_cfg<C, true, false, false>(p, s);
+    if (!async) return launch_bwd_cfg<C, false, true>(p, s);
+    return bias ? launch_bwd_cfg<C, true, true>(p, s) : launch_bwd_cfg<C, true, false>(p, s);
 }
 
 // a warp's rows must be addressable with 32-bit byte offsets from its first row
@@ -954,23 +936,16 @@ cudaError_t launch_scan_unitary_fwd(const ScanFwdParams& p_, cudaStream_t stream
     ScanFwdParams p = p_;
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
-    const ScanOptions& o = scan_options();
-    const bool async = !o.force_plain && (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) &&
-                       aligned16(p.theta) && aligned16(p.u) && aligned16(p.dt) && aligned16(p.z) &&
-                       (p.y == nullptr || aligned16(p.y)) && offsets_fit(p.ld_theta, 128);
-    const bool fast = o.fast_trig != 0;
+    const bool async = (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) && aligned16(p.theta) &&
+                       aligned16(p.u) && aligned16(p.dt) && aligned16(p.z) && (p.y == nullptr || aligned16(p.y)) &&
+                       offsets_fit(p.ld_theta, 128);
     const int N = p.N;
-    if (N <= 4) return launch_fwd_sel<FwdCfg<4, 1, 32, 2, 4>>(p, async, fast, stream);
-    if (N <= 8) return launch_fwd_sel<FwdCfg<8, 1, 32, 2, 4>>(p, async, fast, stream);
-    if (N <= 16) {
-        if (o.variant == 1) return launch_fwd_sel<FwdCfg<8, 2, 32, 2, 4>>(p, async, fast, stream);
-        if (o.variant == 2) return launch_fwd_sel<FwdCfg<16, 1, 64, 2, 4>>(p, async, fast, stream);
-        if (o.variant == 3) return launch_fwd_sel<FwdCfg<16, 1, 32, 3, 4>>(p, async, fast, stream);
-        return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 4>>(p, async, fast, stream);
-    }
-    if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 32, 2, 4>>(p, async, fast, stream);
-    if (N <= 64) return launch_fwd_sel<FwdCfg<32, 2, 32, 2, 4>>(p, async, fast, stream);
-    if (N <= 128) return launch_fwd_sel<FwdCfg<32, 4, 32, 2, 2>>(p, async, fast, stream);
+    if (N <= 4) return launch_fwd_sel<FwdCfg<4, 1, 32, 2, 4>>(p, async, stream);
+    if (N <= 8) return launch_fwd_sel<FwdCfg<8, 1, 32, 2, 4>>(p, async, stream);
+    if (N <= 16) return launch_fwd_sel<FwdCfg<16, 1, 32, 2, 4>>(p, async, stream);
+    if (N <= 32) return launch_fwd_sel<FwdCfg<32, 1, 32, 2, 4>>(p, async, stream);
+    if (N <= 64) return launch_fwd_sel<FwdCfg<32, 2, 32, 2, 4>>(p, async, stream);
+    if (N <= 128) return launch_fwd_sel<FwdCfg<32, 4, 32, 2, 2>>(p, async, stream);
     return cudaErrorInvalidValue;
 }
 
@@ -980,26 +955,18 @@ cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p_, cudaStream_t stream
     p.status = device_status_ptr();
     if (!p.status) return cudaErrorInvalidSymbol;
     if (p.ld_dtheta != p.ld_theta) return cudaErrorInvalidValue;
-    const ScanOptions& o = scan_options();
-    const bool async = !o.force_plain && (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) &&
-                       aligned16(p.theta) && aligned16(p.dtheta) && aligned16(p.u) && aligned16(p.dt) &&
-                       aligned16(p.z) && aligned16(p.gy) && aligned16(p.du) && aligned16(p.ddt) &&
-                       aligned16(p.dz) && offsets_fit(p.ld_theta, 128);
-    const bool fast = o.fast_trig != 0;
+    const bool async = (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) && aligned16(p.theta) &&
+                       aligned16(p.dtheta) && aligned16(p.u) && aligned16(p.dt) && aligned16(p.z) &&
+                       aligned16(p.gy) && aligned16(p.du) && aligned16(p.ddt) && aligned16(p.dz) &&
+                       offsets_fit(p.ld_theta, 128);
     const int N = p.N;
-    if (N <= 4) return launch_bwd_sel<BwdCfg<4, 1, 32, 32, 2, 2>>(p, async, fast, stream);
-    if (N <= 8) return launch_bwd_sel<BwdCfg<8, 1, 32, 32, 2, 2>>(p, async, fast, stream);
-    if (N <= 16) {
-        if (o.variant == 1) return launch_bwd_sel<BwdCfg<8, 2, 32, 32, 2, 2>>(p, async, fast, stream);
-        if (o.variant == 2) return launch_bwd_sel<BwdCfg<16, 1, 64, 32, 2, 2>>(p, async, fast, stream);
-        if (o.variant == 3) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 3, 2>>(p, async, fast, stream);
-
-        // one-warp blocks: a finished warp is replaced at once (measured 9.55 ms against 10.2 ms with two-warp blocks)
-        return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 1>>(p, async, fast, stream);
-    }
-    if (N <= 32) return launch_bwd_sel<BwdCfg<32, 1, 32, 32, 2, 2>>(p, async, fast, stream);
-    if (N <= 64) return launch_bwd_sel<BwdCfg<32, 2, 32, 32, 2, 2>>(p, async, fast, stream);
-    if (N <= 128) return launch_bwd_sel<BwdCfg<32, 4, 32, 32, 2, 2>>(p, async, fast, stream);
+    if (N <= 4) return launch_bwd_sel<BwdCfg<4, 1, 32, 32, 2, 2>>(p, async, stream);
+    if (N <= 8) return launch_bwd_sel<BwdCfg<8, 1, 32, 32, 2, 2>>(p, async, stream);
+    // one-warp blocks: a finished warp is replaced at once (measured 9.55 ms against 10.2 ms with two-warp blocks)
+    if (N <= 16) return launch_bwd_sel<BwdCfg<16, 1, 32, 32, 2, 1>>(p, async, stream);
+    if (N <= 32) return launch_bwd_sel<BwdCfg<32, 1, 32, 32, 2, 2>>(p, async, stream);
+    if (N <= 64) return launch_bwd_sel<BwdCfg<32, 2, 32, 32, 2, 2>>(p, async, stream);
+    if (N <= 128) return launch_bwd_sel<BwdCfg<32, 4, 32, 32, 2, 2>>(p, async, stream);
     return cudaErrorInvalidValue;
 }
 
@@ -1007,6 +974,7 @@ cudaError_t launch_reduce_param_grads(const ReduceParams& p, cudaStream_t stream
     const long long tail = (long long)p.D + (p.dx_bias ? (long long)p.D * p.N : 0);
     const unsigned blocks = (unsigned)(p.N + (tail + 255) / 256);
     reduce_param_grads_kernel<<<blocks, 256, 0, stream>>>(p);
+    count_launch();
     return cudaGetLastError();
 }
 

@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#include "host_common.cuh"
+
 namespace aussm {
 
 // All row pointers address element t = 0 of the launch; a row is L floats
@@ -87,20 +89,6 @@ struct ReduceParams {
     float* dx_bias;            // (D, N) or nullptr
     int batch, D, N;
 };
-
-// Tuning knobs read at launch time (set through aussm_b200_set_option()).
-struct ScanOptions {
-    int fast_trig;   // 1: special-function-unit sin/cos instead of the accurate polynomial
-    int force_plain; // 1: never use bulk copies (plain coalesced loads / stores)
-    int variant;     // tile-shape variant index, 0 = default
-    int blocks_per_sm; // > 0: pad the dynamic shared memory so that exactly this many blocks fit on an SM
-};
-ScanOptions& scan_options();
-
-// Address of the device status word of the current device (nullptr on failure),
-// and a synchronising read-and-clear of it.
-int* device_status_ptr();
-cudaError_t read_and_clear_device_status(cudaStream_t stream, int* value);
 
 cudaError_t launch_scan_unitary_fwd(const ScanFwdParams& p, cudaStream_t stream);
 cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p, cudaStream_t stream);

@@ -70,18 +70,18 @@ class HostBatchStep:
     stream waits for the last copy, so a synchronize (or an event recorded on it) covers the whole step.
     """
 
-    def __init__(self, device, chunk: Optional[int] = None, short_edges: bool = True, compute_streams: int = 1):
+    def __init__(self, device, chunk: Optional[int] = None, short_edges: bool = True):
         self.device = torch.device(device)
         self.chunk = chunk
         self.short_edges = short_edges
         self.s_in = torch.cuda.Stream(self.device)
-        # compute_streams = 2 lets two compute streams take the chunks in turn (kernels of neighbouring chunks could
-        # fill each other's gaps); measured slower than one stream (146 against 136 ms on the benchmark step), so one
-        # is the default
-        self.s_cmp = [torch.cuda.Stream(self.device) for _ in range(2 if compute_streams >= 2 else 1)]
+        # one compute stream: two streams taking the chunks in turn measured slower (146 against 136 ms on the
+        # benchmark step)
+        self.s_cmp = [torch.cuda.Stream(self.device)]
         self.s_out = torch.cuda.Stream(self.device)
         self._bufs = None
         self._shape = None
+        self.kernel_launches_last_step = 0     # this library's kernels queued by the last step() call
 
     def _prepare(self, b, d, l, chunk):
         key = (b, d, l, chunk)
@@ -91,7 +91,12 @@ class HostBatchStep:
         mk = lambda: torch.empty(chunk, d, l, device=self.device, dtype=torch.float32)
         self._bufs = [{k: mk() for k in _SEQ} for _ in range(2)]
 
-    def step(self, inputs: Dict[str, Tensor], outputs: Dict[str, Tensor]) -> None:
+    def step(self, inputs: Dict[str, Tensor], outputs: Dict[str, Tensor], copies_only: bool = False) -> None:
+        """``copies_only=True`` queues the same host<->device copies in the same chunks and order but no
+        arithmetic (the outputs then hold copies of the inputs): the time of that is what the host and the
+        links allow this step, whatever the kernels do."""
+        from . import _lib
+        launches0 = _lib.load().aussm_b200_kernel_launches()
         u = inputs["u"]
         b, d, l = u.shape
         chunk = self.chunk or max(1, b // 8)
@@ -136,11 +141,15 @@ class HostBatchStep:
             par = params[c % len(self.s_cmp)]
             with torch.cuda.stream(sc):
                 sc.wait_event(in_ready[i])
-                leaves = [buf[k][: hi - lo].detach().requires_grad_(True) for k in ("u", "dt", "z")]
-                y = ops.ssm_adaptive_interface(leaves[0], leaves[1], par[0], par[1], par[2], par[3], par[4],
-                                               leaves[2], unitary=True)
-                y.backward(buf["gy"][: hi - lo])
-                res = {"y": y.detach(), "u": leaves[0].grad, "dt": leaves[1].grad, "z": leaves[2].grad}
+                if copies_only:
+                    res = {"y": buf["gy"][: hi - lo], "u": buf["u"][: hi - lo], "dt": buf["dt"][: hi - lo],
+                           "z": buf["z"][: hi - lo]}
+                else:
+                    leaves = [buf[k][: hi - lo].detach().requires_grad_(True) for k in ("u", "dt", "z")]
+                    y = ops.ssm_adaptive_interface(leaves[0], leaves[1], par[0], par[1], par[2], par[3], par[4],
+                                                   leaves[2], unitary=True)
+                    y.backward(buf["gy"][: hi - lo])
+                    res = {"y": y.detach(), "u": leaves[0].grad, "dt": leaves[1].grad, "z": leaves[2].grad}
                 done = sc.record_event()
                 in_free[i] = done
             with torch.cuda.stream(self.s_out):
@@ -148,10 +157,16 @@ class HostBatchStep:
                 for k, t in res.items():
                     t.record_stream(self.s_out)
                     outputs[k][lo:hi].copy_(t, non_blocking=True)
+                if copies_only:
+                    # the copies out must finish before the next copy in reuses this buffer set
+                    in_free[i] = self.s_out.record_event()
         with torch.cuda.stream(self.s_out):
             for sc in self.s_cmp:
                 self.s_out.wait_stream(sc)
             for j, k in enumerate(_PARAMS):
+                if copies_only:
+                    outputs[k].copy_(params[0][j].detach(), non_blocking=True)
+                    continue
                 grads = [par[j].grad for par in params if par[j].grad is not None]
                 for g in grads:
                     g.record_stream(self.s_out)
@@ -159,3 +174,4 @@ class HostBatchStep:
                 outputs[k].copy_(total, non_blocking=True)
         cur.wait_stream(self.s_out)
         cur.wait_stream(self.s_in)
+        self.kernel_launches_last_step = int(_lib.load().aussm_b200_kernel_launches() - launches0)

@@ -3,7 +3,7 @@
 The reference's blocks run their ``nn.Linear`` projections (in_proj, out_proj, x_proj, dt_proj; aussm.py:735-761,
 :826-848) as float32 matrix products, which the library routes to SIMT SGEMM kernels (about 45 TFLOP/s on B200).
 ``SplitLinear`` is ``nn.Linear`` (same parameters, same ``state_dict`` keys) whose forward and backward products go
-through the three-term split GEMM of this library (``aussm_b200_gemm_tf32x3``: float32-level accuracy on tcgen05),
+through the three-term split GEMM of this library (``aussm_b200_gemm_split3``: float32-level accuracy on tcgen05),
 for CUDA float32 inputs whose feature sizes are multiples of 4; anything else takes ``F.linear``.
 """
 from __future__ import annotations

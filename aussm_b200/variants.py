@@ -31,10 +31,10 @@ __all__ = ["scan_complex", "project", "ssm_adaptive_complex", "ssm_adaptive_prea
 def _gemm(A, a_mn, a_b, B, b_mn, b_b, C, M, N, K, batches, reduce, beta=0):
     lib = _lib.load()
     with torch.cuda.device(C.device):
-        ws = _workspace(lib.aussm_b200_gemm_tf32x3_workspace_bytes(M, N, K, batches, a_b, b_b), C.device)
-        rc = lib.aussm_b200_gemm_tf32x3(_ptr(A), a_mn, a_b, _ptr(B), b_mn, b_b, _ptr(C), M, N, K, batches, reduce, beta,
+        ws = _workspace(lib.aussm_b200_gemm_split3_workspace_bytes(M, N, K, batches, a_mn, a_b, b_mn, b_b), C.device)
+        rc = lib.aussm_b200_gemm_split3(_ptr(A), a_mn, a_b, _ptr(B), b_mn, b_b, _ptr(C), M, N, K, batches, reduce, beta,
                                         _ptr(ws), ws.numel(), _stream(C))
-    _lib.check(rc, "gemm_tf32x3")
+    _lib.check(rc, "gemm_split3")
 
 
 class _Projection(torch.autograd.Function):

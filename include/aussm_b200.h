@@ -2,9 +2,9 @@
  * selective-scan operators.
  *
  * Every entry point takes plain device pointers, sizes and a CUDA stream; it
- * allocates nothing on the device except where noted (the cuBLAS handle of the
- * drop-in operators is created on their first call per device), enqueues its
- * kernels on `stream` and returns without synchronising.  Return value: 0 on
+ * allocates nothing on the device (scratch is always a caller-owned workspace),
+ * enqueues its kernels on `stream` and returns without synchronising.  The
+ * library depends on the CUDA runtime only (no cuBLAS or other library kernels).  Return value: 0 on
  * success, a negative AUSSM_E* code otherwise; aussm_b200_last_error() then
  * describes the failure (thread-local string).
  *
@@ -34,7 +34,7 @@ extern "C" {
 #define AUSSM_OK 0
 #define AUSSM_EINVAL (-1)     /* bad size, null pointer, unsupported state count */
 #define AUSSM_EWORKSPACE (-2) /* workspace missing or too small */
-#define AUSSM_ECUDA (-3)      /* a CUDA runtime or cuBLAS call failed */
+#define AUSSM_ECUDA (-3)      /* a CUDA runtime call failed */
 #define AUSSM_EDEVICE (-4)    /* a kernel reported a failure through the device status word */
 
 #define AUSSM_MAX_STATES 128  /* largest N the kernels are instantiated for */
@@ -52,11 +52,17 @@ const char* aussm_b200_last_error(void);
  * for a bulk copy (its outputs are then invalid). */
 int aussm_b200_device_status(aussm_stream_t stream);
 
-/* Tuning / measurement switches: name in {"fast_trig", "force_plain", "variant",
- * "blocks_per_sm", "gemm_tile" (steps per time window of the drop-in operators),
- * "gemm_backend" (0: tensor cores, FP16 parts where the pitches allow; 1: library
- * SGEMM; 2: tensor cores, TF32 parts), "gemm_pair" (1: two-CTA tiles, 0: one CTA
- * per tile, the default), "gemm_probe" (measurement only)}.  Returns AUSSM_EINVAL for an unknown name. */
+/* Number of kernels this library has launched in this process so far (all
+ * threads, all devices): the difference around a region counts its launches. */
+unsigned long long aussm_b200_kernel_launches(void);
+
+/* Per-thread option of the calling thread.  The only name is "window_steps":
+ * steps per time window of the drop-in operators (rounded up to a multiple of
+ * 64; 0 = automatic, about 2 GiB of phases per window).  It decides the layout
+ * of the workspace and of a kept-phase buffer, so the size queries and the
+ * forward / backward calls of one operator invocation must see the same value
+ * (a kept-phase backward call refuses a buffer written under another value).
+ * Returns AUSSM_EINVAL for an unknown name. */
 int aussm_b200_set_option(const char* name, int value);
 
 /* ---- scan core: the phase tensor theta is an input ----------------------
@@ -98,10 +104,17 @@ int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const 
  *
  *  - Limit: B*D*(5*N+1)*4 bytes <= AUSSM_STATIC_SCRATCH_BYTES, otherwise
  *    AUSSM_EWORKSPACE is returned and nothing is launched.
- *  - Cost: every GPU on which this library is loaded holds the array until the
- *    process exits, whether or not this function is ever called.
- *  - The first call on a device looks up the array's device address (no
- *    allocation); make that first call before starting any stream capture.
+ *  - Cost: the array is part of the library's device code.  The CUDA runtime
+ *    loads device code lazily by default, so a GPU holds the 4 MiB from the
+ *    first call of this function on it (from library load when
+ *    CUDA_MODULE_LOADING=EAGER is set) until the process exits.
+ *  - First call on a device: it makes the runtime load that code (which may
+ *    reserve device memory and synchronise the device) and looks up the
+ *    array's device address.  Make one warm-up call per device BEFORE the
+ *    region in which allocation or synchronisation is off limits, and before
+ *    starting any stream capture; every later call on that device only
+ *    enqueues two kernels.  The address is cached per device ordinal for the
+ *    life of the process (devices 0..63; a cudaDeviceReset invalidates it).
  *  - All calls on a device share the one array.  Each call overwrites every
  *    word it later reads, so earlier contents never matter, but two calls whose
  *    kernels overlap on the GPU (different streams) race on it: serialise them. */
@@ -120,15 +133,18 @@ int aussm_b200_scan_unitary_bwd_static(const float* grad_y, const float* gh1_re,
  * (reference: the per-row loops of ssm_adaptive_unitary_forward.cu:83-110 and
  * the atomics of ssm_adaptive_unitary_backward.cu:419-490), exposed on its own.
  * C[M x N] (+)= A * B^T in the sense  C[m][n] = sum_k A(m,k) B(n,k), computed on
- * the tcgen05 tensor cores as a three-term TF32 split (float32-level accuracy).
+ * the tcgen05 tensor cores as a three-term product of FP16 hi/lo parts taken
+ * after a power-of-two scaling by each tensor's largest magnitude (float32-level
+ * accuracy over the whole float32 range).
  * Packed operands: x_mn_major == 0: stored (rows, K), K contiguous;
  * x_mn_major == 1: stored (K, rows), rows contiguous.  `batches` entries follow
  * each other for an operand with x_batched != 0; a non-batched operand is shared.
  * reduce_batches != 0: one C = sum over batches; else C holds `batches` M x N
- * results.  beta: 0 overwrite, 1 accumulate.  K, M (A) / N (B) row lengths must
- * be multiples of 4 floats. */
-size_t aussm_b200_gemm_tf32x3_workspace_bytes(int M, int N, int K, int batches, int a_batched, int b_batched);
-int aussm_b200_gemm_tf32x3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
+ * results.  beta: 0 overwrite, 1 accumulate.  Any M, N, K and alignment: the
+ * hi/lo parts are written into the workspace with 16-byte aligned rows. */
+size_t aussm_b200_gemm_split3_workspace_bytes(int M, int N, int K, int batches, int a_mn_major, int a_batched,
+                                              int b_mn_major, int b_batched);
+int aussm_b200_gemm_split3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
                            int b_batched, float* C, int M, int N, int K, int batches, int reduce_batches, int beta,
                            void* workspace, size_t workspace_bytes, aussm_stream_t stream);
 

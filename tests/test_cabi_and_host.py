@@ -40,7 +40,7 @@ def test_workspace_queries_and_options():
     assert lib.aussm_b200_scan_unitary_bwd_workspace_bytes(16, 1024, 16, 16384) == 16 * 1024 * 81 * 4
     assert lib.aussm_b200_set_option(b"no_such_option", 1) != 0
     assert b"unknown option" in lib.aussm_b200_last_error()
-    assert lib.aussm_b200_set_option(b"fast_trig", 0) == 0
+    assert lib.aussm_b200_set_option(b"window_steps", 0) == 0
 
 
 def test_no_cpu_fallback():

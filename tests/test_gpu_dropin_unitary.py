@@ -101,10 +101,10 @@ def test_windowed_pipeline_and_chunked_front_end_agree_with_one_shot():
     inp = model_like_inputs(77, 2, 16, 16, 328)
     y0, g0 = _interface_grads(inp)
     try:
-        _lib.set_option("gemm_tile", 64)              # six windows instead of one
+        _lib.set_option("window_steps", 64)              # six windows instead of one
         y1, g1 = _interface_grads(inp)
     finally:
-        _lib.set_option("gemm_tile", 0)
+        _lib.set_option("window_steps", 0)
     y2, g2 = _interface_grads(inp, max_parallel_length=80)   # python-level chunks chained through autograd
     for y, g in ((y1, g1), (y2, g2)):
         assert scaled_error(y, y0) < 2e-5
@@ -123,7 +123,7 @@ def test_kept_phases_give_bit_identical_gradients():
     old = ops.keep_phases
     try:
         for tile in (0, 64):
-            _lib.set_option("gemm_tile", tile)
+            _lib.set_option("window_steps", tile)
             ops.keep_phases = False
             y0, g0 = _interface_grads(inp)
             ops.keep_phases = True
@@ -140,7 +140,7 @@ def test_kept_phases_give_bit_identical_gradients():
             assert torch.equal(p, q)
     finally:
         ops.keep_phases = old
-        _lib.set_option("gemm_tile", 0)
+        _lib.set_option("window_steps", 0)
     assert aussm_b200.device_status() == 0
 
 

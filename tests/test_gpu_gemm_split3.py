@@ -1,5 +1,4 @@
-"""The tcgen05 three-term split GEMM (FP16 parts by default, TF32 parts as option or when a pitch is not a
-multiple of 8) against a float64 product (through the C ABI)."""
+"""The tcgen05 three-term split GEMM (FP16 hi/lo parts) against a float64 product, through the C ABI."""
 import pytest
 import torch
 
@@ -11,11 +10,11 @@ pytestmark = pytest.mark.gpu
 
 def _gemm(A, a_mn, a_b, B, b_mn, b_b, C, M, N, K, batches, reduce, beta):
     lib = _lib.load()
-    nbytes = lib.aussm_b200_gemm_tf32x3_workspace_bytes(M, N, K, batches, a_b, b_b)
+    nbytes = lib.aussm_b200_gemm_split3_workspace_bytes(M, N, K, batches, a_mn, a_b, b_mn, b_b)
     ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
-    rc = lib.aussm_b200_gemm_tf32x3(A.data_ptr(), a_mn, a_b, B.data_ptr(), b_mn, b_b, C.data_ptr(), M, N, K, batches,
+    rc = lib.aussm_b200_gemm_split3(A.data_ptr(), a_mn, a_b, B.data_ptr(), b_mn, b_b, C.data_ptr(), M, N, K, batches,
                                     reduce, beta, ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
-    _lib.check(rc, "gemm_tf32x3")
+    _lib.check(rc, "gemm_split3")
     assert aussm_b200.device_status() == 0
 
 
@@ -36,27 +35,17 @@ CASES = [
     (384, 260, 64, 3, 0, 1, 0),       # shared A, batched B, one output per batch (theta = x u_b)
     (320, 128, 72, 3, 1, 1, 1),       # reduction over the batch (dx)
     (132, 200, 256, 2, 0, 1, 0),      # du-like
+    (130, 75, 37, 2, 0, 1, 0),        # nothing a multiple of 4: scalar split loads, scalar stores of C
+    (61, 259, 129, 3, 1, 1, 1),
+    (7, 5, 3, 1, 0, 0, 0),
 ]
-
-
-@pytest.fixture(params=["f16", "tf32", "f16-pair", "tf32-pair"])
-def parts(request):
-    """gemm_backend 0: FP16 parts where every pitch is a multiple of 8; 2: TF32 parts always;
-    gemm_pair 0: one CTA per tile (default), 1: two-CTA tiles (tcgen05.mma.cta_group::2)"""
-    _lib.set_option("gemm_backend", 0 if request.param.startswith("f16") else 2)
-    _lib.set_option("gemm_pair", 1 if request.param.endswith("pair") else 0)
-    yield request.param
-    _lib.set_option("gemm_backend", 0)
-    _lib.set_option("gemm_pair", 0)
 
 
 @pytest.mark.parametrize("majors", [(0, 0), (0, 1), (1, 0), (1, 1)])
 @pytest.mark.parametrize("case", CASES)
-def test_gemm_matches_float64(case, majors, parts):
+def test_gemm_matches_float64(case, majors):
     M, N, K, batches, a_b, b_b, reduce = case
     a_mn, b_mn = majors
-    if (a_mn and M % 4) or (b_mn and N % 4) or K % 4:
-        pytest.skip("row length not a multiple of 4 floats")
     gen = torch.Generator().manual_seed(M * 7 + N * 3 + K + batches + a_mn * 2 + b_mn)
     A_log, A = _operand(M, K, a_mn, batches if a_b else 1, gen)
     B_log, Bm = _operand(N, K, b_mn, batches if b_b else 1, gen)
@@ -74,7 +63,7 @@ def test_gemm_matches_float64(case, majors, parts):
         assert err <= 3e-6 * scale, f"beta={beta}: max error {err:.3e} on scale {scale:.3e}"
 
 
-def test_large_k_accuracy_is_float32_like(parts):
+def test_large_k_accuracy_is_float32_like():
     M, N, K = 256, 256, 4096
     gen = torch.Generator().manual_seed(1)
     A = torch.randn(M, K, generator=gen)
@@ -84,7 +73,7 @@ def test_large_k_accuracy_is_float32_like(parts):
     want = A.double() @ B.double().T
     err_tc = (C.cpu().double() - want).abs().max().item()
     err_fp32 = ((A.cuda() @ B.cuda().T).cpu().double() - want).abs().max().item()
-    print(f"K=4096: {parts} parts max error {err_tc:.3e}, float32 matmul {err_fp32:.3e}")
+    print(f"K=4096: split GEMM max error {err_tc:.3e}, float32 matmul {err_fp32:.3e}")
     assert err_tc <= 4 * err_fp32 + 1e-4
 
 
@@ -99,7 +88,6 @@ def test_f16_parts_keep_accuracy_over_the_float32_range(scales):
     A[::3] *= 1e-6                                # rows far below the tensor's maximum
     B[:, ::5] *= 1e-4
     C = torch.empty(M, N, device="cuda")
-    _lib.set_option("gemm_backend", 0)
     _gemm(A.cuda(), 0, 0, B.cuda(), 0, 0, C, M, N, K, 1, 0, 0)
     want = A.double() @ B.double().T
     got = C.cpu().double()
@@ -109,3 +97,29 @@ def test_f16_parts_keep_accuracy_over_the_float32_range(scales):
     ref = (((A.cuda() @ B.cuda().T).cpu().double() - want).abs() / row_scale).max().item()
     print(f"scales {scales}: f16 parts {rel:.3e}, float32 matmul {ref:.3e} (relative to sum |a||b|)")
     assert rel <= 5e-7
+
+
+def test_misaligned_base_pointers_take_the_scalar_paths():
+    """Operands and output that start 4 bytes into a buffer (not 16-byte aligned)."""
+    M, N, K = 96, 88, 72
+    gen = torch.Generator().manual_seed(9)
+    A = torch.randn(M, K, generator=gen)
+    B = torch.randn(N, K, generator=gen)
+    Ad = torch.empty(M * K + 1, device="cuda")[1:].view(M, K).copy_(A)
+    Bd = torch.empty(N * K + 1, device="cuda")[1:].view(N, K).copy_(B)
+    Cd = torch.zeros(M * N + 1, device="cuda")[1:].view(M, N)
+    assert Ad.data_ptr() % 16 and Cd.data_ptr() % 16
+    _gemm(Ad, 0, 0, Bd, 0, 0, Cd, M, N, K, 1, 0, 0)
+    want = A.double() @ B.double().T
+    err = (Cd.cpu().double() - want).abs().max().item()
+    assert err <= 3e-6 * want.abs().max().item()
+
+
+def test_launch_counter_counts_this_librarys_kernels():
+    lib = _lib.load()
+    A = torch.randn(64, 64, device="cuda")
+    C = torch.empty(64, 64, device="cuda")
+    before = lib.aussm_b200_kernel_launches()
+    _gemm(A, 0, 0, A, 0, 0, C, 64, 64, 64, 1, 0, 0)
+    # two maximum passes, two split passes, one GEMM
+    assert lib.aussm_b200_kernel_launches() - before == 5
