@@ -10,6 +10,7 @@ CUDA device and the library must be built.
 """
 from __future__ import annotations
 
+import os
 import sys
 import types
 from typing import Optional, Tuple
@@ -64,9 +65,25 @@ def _workspace(nbytes: int, device) -> Tensor:
 
 
 def device_status(device=None) -> int:
-    """Synchronise the current stream and return (and clear) the kernels' status word."""
-    stream = torch.cuda.current_stream(device).cuda_stream
-    return int(_lib.load().aussm_b200_device_status(stream))
+    """Synchronise the current stream of `device` and return (and clear) the status word of that device's kernels.
+
+    0 = every kernel ran to completion; 1 = a kernel gave up on a bounded wait (its outputs are then invalid).
+    The operators do not poll this word themselves unless ``check_device_status`` is set, because reading it
+    synchronises the stream."""
+    with torch.cuda.device(device):            # the word is per device: read the one that owns the stream
+        stream = torch.cuda.current_stream().cuda_stream
+        return int(_lib.load().aussm_b200_device_status(stream))
+
+
+# Opt-in polling of the device status word: when true (or when the environment variable
+# AUSSM_B200_CHECK_STATUS=1 is set at import), every drop-in operator call and every training step synchronises
+# its stream once and raises if a kernel reported a timed-out wait, instead of handing on invalid values.
+check_device_status = os.environ.get("AUSSM_B200_CHECK_STATUS", "0") == "1"
+
+
+def _poll_status(what: str, device) -> None:
+    if check_device_status and device_status(device) != 0:
+        raise RuntimeError(f"{what}: a kernel gave up on a bounded wait (device status word set); outputs are invalid")
 
 
 # ---------------------------------------------------------------------------
@@ -106,6 +123,7 @@ def _unitary_forward(u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h
             _ptr(z), _ptr(h_re), _ptr(h_im), _ptr(y), _ptr(o_re), _ptr(o_im), b, d, n, l, _ptr(ws), ws.numel(),
             _stream(u))
     _lib.check(rc, "ssm_adaptive_unitary")
+    _poll_status("ssm_adaptive_unitary", u.device)
     return y, o_re, o_im
 
 
@@ -148,6 +166,7 @@ def _unitary_backward(grad_y, g_re, g_im, u, dt, x, x_bias, B_r, B_theta, C_r, C
         else:
             rc = lib.aussm_b200_unitary_bwd(*args, _stream(u))
     _lib.check(rc, "ssm_adaptive_backward_unitary")
+    _poll_status("ssm_adaptive_backward_unitary", u.device)
     return du, ddt, dx, dxb, dBr, dBt, dCr, dCt, dD, dz, dh_re, dh_im
 
 
@@ -210,6 +229,7 @@ class _UnitaryKeep(torch.autograd.Function):
                 _ptr(D), _ptr(z), _ptr(h_re), _ptr(h_im), _ptr(y), _ptr(o_re), _ptr(o_im), b, d, n, l, _ptr(ws),
                 ws.numel(), _ptr(keep), keep.numel(), _stream(u))
         _lib.check(rc, "ssm_adaptive_unitary (phases kept)")
+        _poll_status("ssm_adaptive_unitary (phases kept)", u.device)
         ctx.save_for_backward(u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, D, z, h_re, h_im, o_re, o_im)
         ctx.keep = keep
         return y, o_re, o_im

@@ -34,9 +34,10 @@ def shard_range(total: int, rank: int, world: int):
 
 
 def allreduce_gradients(params: Iterable[torch.nn.Parameter], world: int, bucket_bytes: int = 64 << 20,
-                        group=None) -> int:
-    """Average the gradients over ranks with one all-reduce per flat bucket; returns the number of collectives.
-    Parameters without a gradient contribute zeros, so that every rank issues the same collectives."""
+                        group=None, average: bool = True) -> int:
+    """Sum the gradients over ranks with one all-reduce per flat bucket and, with ``average``, divide by the
+    number of ranks; returns the number of collectives.  Parameters without a gradient contribute zeros, so
+    that every rank issues the same collectives."""
     if world <= 1:
         return 0
     params = [p for p in params if p.requires_grad]
@@ -54,7 +55,8 @@ def allreduce_gradients(params: Iterable[torch.nn.Parameter], world: int, bucket
             flats.append(torch.view_as_real(g).reshape(-1) if g.is_complex() else g.reshape(-1))
         flat = torch.cat([f.float() for f in flats])
         dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
-        flat /= world
+        if average:
+            flat /= world
         off = 0
         for p, f in zip(bucket, flats):
             n = f.numel()
@@ -119,22 +121,31 @@ def make_config(config: int, device, rank: int, world: int, scale: float = 1.0):
         tokens = gb * l
     else:
         raise ValueError("config must be 3 or 4")
-    return model, batch, loss_fn, tokens, hi - lo
+    return model, batch, loss_fn, tokens, hi - lo, gb
 
 
-def train_step(model, opt, x, y, loss_fn, world: int, micro_batch: int = 0, clip: float = 1.0):
+def train_step(model, opt, x, y, loss_fn, world: int, micro_batch: int = 0, clip: float = 1.0,
+               global_batch: int = 0):
     """Forward, backward (optionally in micro-batches that accumulate gradients), gradient all-reduce,
-    clipping at `clip` (the reference's gradient_clip_val, experiments/all/weather.yaml:63) and optimizer step."""
+    clipping at `clip` (the reference's gradient_clip_val, experiments/all/weather.yaml:63) and optimizer step.
+
+    Every sample weighs 1 / global_batch in the loss whatever shard it is in, and the ranks' gradients are
+    summed: the result equals the single-process gradient of the mean loss also when the shards are uneven
+    (global batch not divisible by the number of ranks).  ``global_batch = 0`` means local batch x world."""
     opt.zero_grad(set_to_none=True)
     n = x.shape[0]
+    gb = global_batch if global_batch > 0 else n * world
     mb = n if micro_batch <= 0 else min(micro_batch, n)
     total = 0.0
     for s in range(0, n, mb):
         out = model(x[s:s + mb])
-        loss = loss_fn(out, y[s:s + mb]) * (min(s + mb, n) - s) / n
+        loss = loss_fn(out, y[s:s + mb]) * (min(s + mb, n) - s) / gb
         loss.backward()
         total += float(loss.detach())
-    ncoll = allreduce_gradients(model.parameters(), world)
+    from . import ops
+    if ops.check_device_status and x.is_cuda:
+        ops._poll_status("train_step", x.device)
+    ncoll = allreduce_gradients(model.parameters(), world, average=False)
     torch.nn.utils.clip_grad_norm_(model.parameters(), clip)
     opt.step()
     return total, ncoll
@@ -155,11 +166,11 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    model, batch, loss_fn, tokens, local_batch = make_config(a.config, dev, rank, world, a.scale)
+    model, batch, loss_fn, tokens, local_batch, gb = make_config(a.config, dev, rank, world, a.scale)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
     x, y = batch()
     for _ in range(a.warmup):
-        train_step(model, opt, x, y, loss_fn, world, a.micro_batch)
+        train_step(model, opt, x, y, loss_fn, world, a.micro_batch, global_batch=gb)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -167,7 +178,7 @@ def main():
     e0.record()
     loss = ncoll = 0
     for _ in range(a.steps):
-        loss, ncoll = train_step(model, opt, x, y, loss_fn, world, a.micro_batch)
+        loss, ncoll = train_step(model, opt, x, y, loss_fn, world, a.micro_batch, global_batch=gb)
     e1.record()
     if world > 1:
         dist.barrier()
@@ -175,7 +186,7 @@ def main():
     ms = max_over_ranks(e0.elapsed_time(e1) / a.steps, dev, world)
     if rank == 0:
         print(json.dumps({"config": a.config, "n_gpus": world, "ms_per_step": ms, "tokens_per_s": tokens / ms * 1e3,
-                          "global_batch": local_batch * world if world > 1 else local_batch, "loss": loss,
+                          "global_batch": gb, "local_batch": local_batch, "loss": loss,
                           "allreduce_calls_per_step": ncoll, "micro_batch": a.micro_batch, "scale": a.scale,
                           "parameters": sum(p.numel() for p in model.parameters()), "data": "synthetic"}), flush=True)
     if world > 1:

@@ -493,15 +493,15 @@ def run_extras(args, dev, world, rank, barrier):
         torch.cuda.empty_cache()
     train = []
     for config, micro, steps in ((3, 0, 3), (4, 4, 1)):
-        model, batch, loss_fn, tokens, local_batch = make_config(config, dev, rank, world)
+        model, batch, loss_fn, tokens, local_batch, gb = make_config(config, dev, rank, world)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
         x, y = batch()
-        train_step(model, opt, x, y, loss_fn, world, micro)
+        train_step(model, opt, x, y, loss_fn, world, micro, global_batch=gb)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
-            loss, ncoll = train_step(model, opt, x, y, loss_fn, world, micro)
+            loss, ncoll = train_step(model, opt, x, y, loss_fn, world, micro, global_batch=gb)
         e1.record()
         barrier()
         ms = max_over_ranks(e0.elapsed_time(e1) / steps, dev, world)

@@ -8,7 +8,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from aussm_b200.train import allreduce_gradients, max_over_ranks, shard_range
+from aussm_b200.train import allreduce_gradients, max_over_ranks, shard_range, train_step
 
 
 def _free_port():
@@ -60,3 +60,44 @@ def test_shards_cover_the_batch_without_overlap():
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
             sizes = [hi - lo for lo, hi in spans]
             assert max(sizes) - min(sizes) <= 1
+
+
+def _uneven_worker(rank, world, port, ret):
+    """Three ranks share a global batch of 7 (shards of 3, 2, 2): the reduced gradient of one step must equal
+    the single-process gradient of the mean loss over all 7 samples."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gb = 7
+        g = torch.Generator().manual_seed(5)
+        x, y = torch.randn(gb, 4, generator=g), torch.randn(gb, 2, generator=g)
+        torch.manual_seed(3)
+        model = torch.nn.Linear(4, 2)
+        single = torch.nn.Linear(4, 2)
+        single.load_state_dict(model.state_dict())
+        loss_fn = lambda out, t: torch.mean((out - t) ** 2)
+        torch.mean((single(x) - y) ** 2).backward()
+        lo, hi = shard_range(gb, rank, world)
+
+        class NoStep:                      # keep the weights: only the gradient is compared
+            def zero_grad(self, set_to_none=True):
+                model.zero_grad(set_to_none=set_to_none)
+
+            def step(self):
+                pass
+
+        train_step(model, NoStep(), x[lo:hi], y[lo:hi], loss_fn, world, micro_batch=2, clip=1e9, global_batch=gb)
+        for p, q in zip(model.parameters(), single.parameters()):
+            torch.testing.assert_close(p.grad, q.grad, rtol=1e-5, atol=1e-6)
+        ret[rank] = hi - lo
+    finally:
+        dist.destroy_process_group()
+
+
+def test_uneven_shards_give_the_single_process_gradient():
+    world = 3
+    port = _free_port()
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_uneven_worker, args=(world, port, ret), nprocs=world, join=True)
+        assert sorted(ret.values()) == [2, 2, 3]

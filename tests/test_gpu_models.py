@@ -83,7 +83,7 @@ def test_reference_parameter_names():
 @pytest.mark.parametrize("config", [3, 4])
 def test_training_step_runs_and_reduces_the_loss(config):
     dev = torch.device("cuda", 0)
-    model, batch, loss_fn, _, _ = make_config(config, dev, 0, 1, scale=0.05 if config == 3 else 0.002)
+    model, batch, loss_fn, _, _, _ = make_config(config, dev, 0, 1, scale=0.05 if config == 3 else 0.002)
     opt = torch.optim.AdamW(model.parameters(), lr=2e-3)
     x, y = batch()
     x, y = x[:4], y[:4]
