@@ -29,10 +29,13 @@ SIGNATURES = {
     "aussm_b200_gemm_split3_workspace_bytes": (_Z, [_I] * 8),
     "aussm_b200_gemm_split3": (_I, [_P, _I, _I, _P, _I, _I, _P] + [_I] * 6 + [_P, _Z, _P]),
     "aussm_b200_unitary_workspace_bytes": (_Z, [_I] * 4),
-    "aussm_b200_scan_complex_ckpt_floats": (_Z, [_I] * 4),
+    "aussm_b200_scan_complex_states_floats": (_Z, [_I] * 4),
     "aussm_b200_scan_complex_bwd_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_scan_complex_fwd": (_I, [_P] * 12 + [_I] * 4 + [_P]),
-    "aussm_b200_scan_complex_bwd": (_I, [_P] * 22 + [_I] * 4 + [_P, _Z, _P]),
+    "aussm_b200_scan_complex_bwd": (_I, [_P] * 23 + [_I] * 4 + [_P, _Z, _P]),
+    "aussm_b200_complex_workspace_bytes": (_Z, [_I] * 5),
+    "aussm_b200_complex_fwd": (_I, [_P] * 3 + [_I] + [_P] * 8 + [_I] * 4 + [_P, _Z, _P]),
+    "aussm_b200_complex_bwd": (_I, [_P] * 5 + [_I] + [_P] * 16 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_selective_scan_ckpt_floats": (_Z, [_I] * 4),
     "aussm_b200_selective_scan_bwd_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_selective_scan_fwd": (_I, [_P] * 8 + [_I] + [_P] * 3 + [_I] * 4 + [_P]),

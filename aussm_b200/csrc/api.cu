@@ -21,13 +21,13 @@ namespace aussm {
 
 namespace {
 thread_local std::string t_last_error;
-thread_local int t_window_steps = 0;   // option "window_steps" of the calling thread (0 = automatic)
+std::atomic<int> g_window_steps{0};    // option "window_steps" (0 = automatic); process-wide, see the header
 std::atomic<unsigned long long> g_launches{0};
 }  // namespace
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
-int window_steps_option() { return t_window_steps; }
+int window_steps_option() { return g_window_steps.load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
     char buf[512];
@@ -97,13 +97,13 @@ Plan make_plan(int B, int D, int N, int L, int window_steps = window_steps_optio
     p.off_part = off;
     off = align_up(off + scan_bwd_partial_floats((long long)B * D, N) * 4, 256);
     p.off_proj = off;    // FP16 hi/lo parts of x, of the u window and of the dtheta window
-    off = align_up(off + proj_scratch_bytes(B, D, N, p.ldw), 256);
+    off = align_up(off + proj_scratch_bytes(B, D, (long long)D * N, p.ldw), 256);
     p.total = off;
     return p;
 }
 
 // The layout of a kept-phase buffer (window length and row pitch) follows from the plan of the forward call,
-// which depends on the calling thread's "window_steps" option.  The forward call notes the layout it used under
+// which depends on the "window_steps" option.  The forward call notes the layout it used under
 // the buffer's address (host side, no device traffic); the backward call refuses a buffer that it finds noted
 // with another layout, so a changed option between the two calls is an error instead of wrong gradients.
 struct KeepLayout {
@@ -168,7 +168,7 @@ int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, flo
     for (int w = 0; w < nwin; ++w) {
         const long long t0 = (long long)w * pl.window;
         const int tl = (int)std::min<long long>(pl.window, a.L - t0);
-        const ProjDims pd = {a.B, a.D, a.N, a.L, pl.ldw, t0, tl};
+        const ProjDims pd = {a.B, a.D, (long long)a.D * a.N, a.L, pl.ldw, t0, tl};
         if (keep) theta_w = keep + (size_t)w * pl.rows * pl.ldw;
         if (int rc = proj_theta(pd, a.u, theta_w, ps, stream)) return rc;
         const bool last = (w == nwin - 1);
@@ -217,7 +217,7 @@ unsigned long long aussm_b200_kernel_launches(void) { return launch_count(); }
 int aussm_b200_set_option(const char* name, int value) {
     if (!name) return AUSSM_EINVAL;
     if (!strcmp(name, "window_steps")) {
-        t_window_steps = value > 0 ? value : 0;
+        g_window_steps.store(value > 0 ? value : 0, std::memory_order_relaxed);
         return AUSSM_OK;
     }
     set_error("unknown option '%s'", name);
@@ -385,8 +385,8 @@ static int unitary_fwd_impl(const float* u, const float* dt, const float* x, con
     float* cur_re = reinterpret_cast<float*>(ws + pl.off_h);
     const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
     ProjScratch ps;
-    proj_scratch_bind(ps, ws + pl.off_proj, B, D, N, pl.ldw);
-    if (int rc = proj_begin(B, D, N, x, ps, (cudaStream_t)stream)) return rc;
+    proj_scratch_bind(ps, ws + pl.off_proj, B, D, (long long)D * N, pl.ldw);
+    if (int rc = proj_begin(D, (long long)D * N, x, ps, (cudaStream_t)stream)) return rc;
     if (keep) keep_note_layout(keep, pl);
     return run_unitary_fwd(a, h0_re, h0_im, y, h1_re ? h1_re : cur_re, h1_im ? h1_im : cur_re + pl.rows, ws, pl, ps,
                            (cudaStream_t)stream, static_cast<float*>(keep));
@@ -466,8 +466,8 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
         if (int rc = keep_check_layout(keep_buf, pl)) return rc;
     }
     ProjScratch ps;
-    proj_scratch_bind(ps, ws + pl.off_proj, B, D, N, pl.ldw);
-    if (int rc = proj_begin(B, D, N, x, ps, stream)) return rc;
+    proj_scratch_bind(ps, ws + pl.off_proj, B, D, (long long)D * N, pl.ldw);
+    if (int rc = proj_begin(D, (long long)D * N, x, ps, stream)) return rc;
 
     // final state: given by the caller, or recomputed by a state-only forward sweep
     const float* hend_re = h1_re;
@@ -484,7 +484,7 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
         const int tl = (int)std::min<long long>(pl.window, L - t0);
         const bool first = (w == nwin - 1);   // first processed = last in time
         const bool final_ = (w == 0);
-        const ProjDims pd = {B, D, N, L, pl.ldw, t0, tl};
+        const ProjDims pd = {B, D, (long long)D * N, L, pl.ldw, t0, tl};
         if (keep) {
             theta_w = keep + (size_t)w * pl.rows * pl.ldw;    // phases of the forward call; dtheta replaces them
             if (int rc = proj_split_u(pd, u, ps, stream)) return rc;

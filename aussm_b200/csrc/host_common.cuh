@@ -13,7 +13,7 @@ void set_error(const char* fmt, ...);
 void count_launch(int n = 1);
 unsigned long long launch_count();
 
-// Per-thread tuning value read by the drop-in operators: steps per time window (0 = automatic).
+// Process-wide tuning value read by the drop-in operators: steps per time window (0 = automatic).
 int window_steps_option();
 
 // Address of the device status word of the current device (nullptr on failure), and a synchronising

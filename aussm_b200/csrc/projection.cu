@@ -12,14 +12,14 @@ namespace {
 size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 }  // namespace
 
-size_t proj_scratch_bytes(int B, int D, int N, long long ldw) {
-    const size_t M = (size_t)D * N, Dp = up((size_t)D, 8);
+size_t proj_scratch_bytes(int B, int D, long long M_, long long ldw) {
+    const size_t M = (size_t)M_, Dp = up((size_t)D, 8);
     const size_t halves = 2 * up(M * Dp, 128) + 2 * up((size_t)B * D * ldw, 128) + 2 * up((size_t)B * M * ldw, 128);
     return halves * 2 + 256;
 }
 
-void proj_scratch_bind(ProjScratch& s, void* base, int B, int D, int N, long long ldw) {
-    const size_t M = (size_t)D * N, Dp = up((size_t)D, 8);
+void proj_scratch_bind(ProjScratch& s, void* base, int B, int D, long long M_, long long ldw) {
+    const size_t M = (size_t)M_, Dp = up((size_t)D, 8);
     char* p = static_cast<char*>(base);
     auto take = [&](size_t halves) {
         void* r = p;
@@ -36,9 +36,8 @@ void proj_scratch_bind(ProjScratch& s, void* base, int B, int D, int N, long lon
     s.Dp = (long long)Dp;
 }
 
-int proj_begin(int B, int D, int N, const float* x, ProjScratch& s, cudaStream_t stream) {
-    (void)B;
-    return split_f16(x, D, 0, s.x_hi, s.x_lo, s.Dp, 0, (long long)D * N, D, 1, s.amax + 0, stream);
+int proj_begin(int D, long long M, const float* x, ProjScratch& s, cudaStream_t stream) {
+    return split_f16(x, D, 0, s.x_hi, s.x_lo, s.Dp, 0, M, D, 1, s.amax + 0, stream);
 }
 
 int proj_split_u(const ProjDims& d, const float* u, ProjScratch& s, cudaStream_t stream) {
@@ -48,7 +47,7 @@ int proj_split_u(const ProjDims& d, const float* u, ProjScratch& s, cudaStream_t
 }
 
 int proj_theta(const ProjDims& d, const float* u, float* theta_w, ProjScratch& s, cudaStream_t stream) {
-    const int M = d.D * d.N;
+    const int M = (int)d.M;
     if (int rc = proj_split_u(d, u, s, stream)) return rc;
     // theta_w[b] (M x tl) = x (M x D, K-major) * u_b (D x tl: K rows, N contiguous -> MN-major)
     const SplitOperand A = {s.x_hi, s.x_lo, 0, s.Dp, 0, s.amax + 0};
@@ -59,7 +58,7 @@ int proj_theta(const ProjDims& d, const float* u, float* theta_w, ProjScratch& s
 
 int proj_adjoints(const ProjDims& d, const float* dtheta_w, float* dx, float* du, bool overwrite_dx, ProjScratch& s,
                   cudaStream_t stream, bool dtheta_amax_known) {
-    const int M = d.D * d.N;
+    const int M = (int)d.M;
     if (int rc = split_f16(dtheta_w, d.ldw, (long long)M * d.ldw, s.dth_hi, s.dth_lo, d.ldw, (long long)M * d.ldw, M,
                            d.tl, d.B, s.amax + 2, stream, dtheta_amax_known))
         return rc;

@@ -20,7 +20,8 @@
 namespace aussm {
 
 struct ProjDims {
-    int B, D, N;          // batch, d_inner, states
+    int B, D;             // batch, d_inner
+    long long M;          // rows of x: d_inner * states (twice that when two streams are projected at once)
     long long L;          // row length of u / du
     long long ldw;        // row pitch of the window workspace (floats; a multiple of 8)
     long long t0;
@@ -29,23 +30,23 @@ struct ProjDims {
 
 // Scratch for the FP16 hi/lo parts of the operands (caller-owned, inside the operator workspace).
 struct ProjScratch {
-    void* x_hi;       // (D*N, Dp) halves, Dp = D rounded up to 8
+    void* x_hi;       // (M, Dp) halves, Dp = D rounded up to 8
     void* x_lo;
     void* u_hi;       // (B, D, ldw)      window of u
     void* u_lo;
-    void* dth_hi;     // (B, D*N, ldw)    window of dtheta
+    void* dth_hi;     // (B, M, ldw)      window of dtheta
     void* dth_lo;
     unsigned* amax;   // bit patterns of max|x|, max|u window|, max|dtheta window|
     long long Dp;
 };
 
 // bytes needed behind ProjScratch for a window pitch ldw
-size_t proj_scratch_bytes(int B, int D, int N, long long ldw);
-void proj_scratch_bind(ProjScratch& s, void* base, int B, int D, int N, long long ldw);
+size_t proj_scratch_bytes(int B, int D, long long M, long long ldw);
+void proj_scratch_bind(ProjScratch& s, void* base, int B, int D, long long M, long long ldw);
 
 // returns 0 or a negative AUSSM_E* code (message set)
 // Splits x (once per operator call).
-int proj_begin(int B, int D, int N, const float* x, ProjScratch& s, cudaStream_t stream);
+int proj_begin(int D, long long M, const float* x, ProjScratch& s, cudaStream_t stream);
 // FP16 parts of the current window of u (proj_theta does this itself; proj_adjoints expects it done).
 int proj_split_u(const ProjDims& d, const float* u, ProjScratch& s, cudaStream_t stream);
 int proj_theta(const ProjDims& d, const float* u, float* theta_w, ProjScratch& s, cudaStream_t stream);

@@ -2,21 +2,28 @@
 //
 // Same decomposition as scan_unitary.cu and scan_s6.cu: one thread per state
 // and channel, sequential in time; one independent warp per 32/NL channels of
-// one batch entry; 32-step tiles staged by coalesced 16-byte asynchronous
+// one batch entry; 16-step tiles staged by coalesced 16-byte asynchronous
 // copies in a two-stage ring.  A thread consumes its own rho and theta rows
 // (like the unitary scan) and the B_j, C_j rows of its batch entry (like the
 // S6 scan).  |lambda| != 1, so the recurrence is not reversible: the forward
-// kernel stores the state at every tile start, the backward kernel recomputes
-// a tile's states from there and walks it in reverse.  drho / dtheta are
-// written in place of rho / theta in the stage and leave with coalesced
-// stores; dB and dC (sums over the channels of a batch entry) use shuffles and
-// vector float atomics, as the reference's kernels do (ssm_adaptive_complex.cu).
+// kernel records the state at every tile start, the backward kernel recomputes
+// a tile's states from there and walks it in reverse.
+//
+// Shared memory is what limits the number of resident warps (each state keeps
+// two streams in flight), so the tiles are short (16 steps) and every cell is
+// used several times: the backward kernel's recomputing pass overwrites the
+// rho / theta cells it has consumed with lambda (the reverse pass then needs no
+// second exponential and sine / cosine), and parks the state before each step
+// in the two column-sum tiles; the reverse pass replaces lambda by drho /
+// dtheta, which leave with coalesced stores, and the parked states by the
+// per-state terms of the column sums.  dB and dC (sums over the channels of a
+// batch entry) use shuffles and vector float atomics, as the reference's
+// kernels do (ssm_adaptive_complex.cu:358-660).
 #include "scan_complex.cuh"
 
 #include <stdint.h>
 
 #include "common.cuh"
-#include "host_common.cuh"
 
 namespace aussm {
 namespace {
@@ -24,7 +31,11 @@ namespace {
 constexpr int T = kCplxTile;
 constexpr int TP = T + 4;
 constexpr int STAGES = 2;
+constexpr int NQ = T / 4;
 constexpr float kLog2e = 1.4426950408889634f;
+
+constexpr int cmaxi(int a, int b) { return a > b ? a : b; }
+constexpr int cmini(int a, int b) { return a < b ? a : b; }
 
 template <int NL_, bool BWD_>
 struct CCfg {
@@ -34,56 +45,61 @@ struct CCfg {
     static constexpr int OWN_ROWS = 64;                           // rho rows then theta rows, one per lane
     static constexpr int BC_ROWS = 4 * NL;                        // B_re, B_im, C_re, C_im
     static constexpr int STAGE_FLOATS = (OWN_ROWS + BC_ROWS) * TP + CPW * AUX * T;
-    // not staged.  forward: s row + p tile.  backward: s, w rows + h_prev (re, im), E and P tiles
-    static constexpr int ROWS = BWD_ ? 2 : 1;
-    static constexpr int TILES = BWD_ ? 4 : 1;
+    // not staged.  forward: s row + p tile.  backward: s, w, d silu(u)/du rows + two tiles (state before each
+    // step, then the per-state terms of the two column sums)
+    static constexpr int ROWS = BWD_ ? 3 : 1;
+    static constexpr int TILES = BWD_ ? 2 : 1;
     static constexpr int SCRATCH_FLOATS = CPW * ROWS * T + TILES * 32 * TP;
     static constexpr int WARP_FLOATS = STAGES * STAGE_FLOATS + SCRATCH_FLOATS;
     static constexpr size_t SMEM_BYTES = (size_t)WARP_FLOATS * sizeof(float);
-    static constexpr int NCH_OWN = OWN_ROWS * (T / 4) / 32;       // 16
-    static constexpr int NCH_BC = BC_ROWS * (T / 4) / 32;         // NL
-    static constexpr int NCH_AUX = (CPW * AUX * (T / 4) + 31) / 32;
-    static constexpr int EPL = CPW * T / 32;
-    static constexpr int VW = EPL < 4 ? EPL : 4;
-    static constexpr int ITERS = EPL / VW;
+    static constexpr int NCH_OWN = OWN_ROWS * NQ / 32;
+    static constexpr int NCH_BC = (BC_ROWS * NQ + 31) / 32;
+    static constexpr int NCH_AUX = (CPW * AUX * NQ + 31) / 32;
+    // per-(channel, step) passes: CPW * T elements over 32 lanes
+    static constexpr int ELEMS = CPW * T;
+    static constexpr int VW = cmaxi(1, cmini(4, ELEMS / 32));
+    static constexpr int ITERS = cmaxi(1, ELEMS / (32 * VW));
 };
 
-// per-lane sources of the 16-byte pieces of one tile (at step 0); nullptr = nothing to copy
+// per-lane sources of the 16-byte pieces of one tile (at step 0 of the launch); nullptr = nothing to copy
 template <class C>
 struct CMap {
     const float* own_ptr[C::NCH_OWN];
     const float* bc_ptr[C::NCH_BC];
     const float* aux_ptr[C::NCH_AUX];
 
-    __device__ __forceinline__ void init(int lane, int nvalid, int N, long long L, const float* rho,
-                                         const float* theta, const float* const* bc_src, long long ch0,
-                                         const float* const* aux_src) {
+    __device__ __forceinline__ void init(int lane, int nvalid, int N, const float* rho_b, const float* theta_b,
+                                         long long ld_lam, int i0, const float* const* bc_src,
+                                         const float* const* aux_src, long long ch0, long long ld_row) {
 #pragma unroll
         for (int i = 0; i < C::NCH_OWN; ++i) {
             const int id = i * 32 + lane;
-            const int row = id / (T / 4), col = id % (T / 4);
+            const int row = id / NQ, col = id % NQ;
             const int w = row % 32;                                // the lane that owns the row
             const int c = w / C::NL, j = w % C::NL;
-            const float* base = row < 32 ? rho : theta;
+            const float* base = row < 32 ? rho_b : theta_b;        // rows of this batch entry
             const bool ok = c < nvalid && j < N;
-            own_ptr[i] = base ? base + ((ch0 + (ok ? c : 0)) * N + (ok ? j : 0)) * L + col * 4 : nullptr;
+            own_ptr[i] = base ? base + ((long long)(i0 + (ok ? c : 0)) * N + (ok ? j : 0)) * ld_lam + col * 4 : nullptr;
         }
 #pragma unroll
         for (int i = 0; i < C::NCH_BC; ++i) {
             const int id = i * 32 + lane;
-            const int row = id / (T / 4), col = id % (T / 4);
-            const int which = row / C::NL, j = row % C::NL;
-            const float* base = bc_src[which];
-            bc_ptr[i] = base ? base + (long long)(j < N ? j : 0) * L + col * 4 : nullptr;
+            const int row = id / NQ, col = id % NQ;
+            bc_ptr[i] = nullptr;
+            if (row < C::BC_ROWS) {
+                const int which = row / C::NL, j = row % C::NL;
+                const float* base = bc_src[which];
+                bc_ptr[i] = base ? base + (long long)(j < N ? j : 0) * ld_row + col * 4 : nullptr;
+            }
         }
 #pragma unroll
         for (int i = 0; i < C::NCH_AUX; ++i) {
             const int id = i * 32 + lane;
-            const int row = id / (T / 4), col = id % (T / 4);
+            const int row = id / NQ, col = id % NQ;
             aux_ptr[i] = nullptr;
             if (row < C::CPW * C::AUX) {
                 const int cc = row / C::AUX, a = row % C::AUX;
-                aux_ptr[i] = aux_src[a] + (ch0 + (cc < nvalid ? cc : 0)) * L + col * 4;
+                aux_ptr[i] = aux_src[a] + (ch0 + (cc < nvalid ? cc : 0)) * ld_row + col * 4;
             }
         }
     }
@@ -91,23 +107,18 @@ struct CMap {
     __device__ __forceinline__ void issue(float* stage, long long t0, int tlen, int lane) const {
         float* bc = stage + C::OWN_ROWS * TP;
         float* aux = bc + C::BC_ROWS * TP;
+        const int col = lane % NQ, r0 = lane / NQ;                 // piece i of this lane: row i * (32 / NQ) + r0
+        constexpr int RPI = 32 / NQ;
+        if (col * 4 < tlen) {
 #pragma unroll
-        for (int i = 0; i < C::NCH_OWN; ++i) {
-            const int id = i * 32 + lane;
-            const int row = id / (T / 4), col = id % (T / 4);
-            if (own_ptr[i] != nullptr && col * 4 < tlen) cp_async16(stage + row * TP + col * 4, own_ptr[i] + t0);
-        }
+            for (int i = 0; i < C::NCH_OWN; ++i)
+                if (own_ptr[i] != nullptr) cp_async16(stage + (i * RPI + r0) * TP + col * 4, own_ptr[i] + t0);
 #pragma unroll
-        for (int i = 0; i < C::NCH_BC; ++i) {
-            const int id = i * 32 + lane;
-            const int row = id / (T / 4), col = id % (T / 4);
-            if (bc_ptr[i] != nullptr && col * 4 < tlen) cp_async16(bc + row * TP + col * 4, bc_ptr[i] + t0);
-        }
+            for (int i = 0; i < C::NCH_BC; ++i)
+                if (bc_ptr[i] != nullptr) cp_async16(bc + (i * RPI + r0) * TP + col * 4, bc_ptr[i] + t0);
 #pragma unroll
-        for (int i = 0; i < C::NCH_AUX; ++i) {
-            const int id = i * 32 + lane;
-            const int row = id / (T / 4), col = id % (T / 4);
-            if (aux_ptr[i] != nullptr && col * 4 < tlen) cp_async16(aux + row * T + col * 4, aux_ptr[i] + t0);
+            for (int i = 0; i < C::NCH_AUX; ++i)
+                if (aux_ptr[i] != nullptr) cp_async16(aux + (i * RPI + r0) * T + col * 4, aux_ptr[i] + t0);
         }
         cp_async_commit();
     }
@@ -131,11 +142,13 @@ __device__ __forceinline__ void lambda4(const float4 r4, const float4 t4, float 
     sincos4(tv, sn, cs);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-        const float m = exp2f(rv[e] * kLog2e);
+        const float m = ex2_ftz(rv[e] * kLog2e);
         lr[e] = m * cs[e];
         li[e] = m * sn[e];
     }
 }
+
+#define AUSSM_F4(v) {(v).x, (v).y, (v).z, (v).w}
 
 // ---------------------------------------------------------------------------
 // Forward
@@ -161,18 +174,27 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
     float* pt = srow + CPW * C::ROWS * T;                   // [32][TP]
     zero_stages<C>(smem, lane);
 
+    float2* rec = (p.states && act) ? reinterpret_cast<float2*>(p.states) + (ch * N + j) * p.states_stride + p.tile0
+                                    : nullptr;
     float hr = 0.f, hi = 0.f;
+    if (rec && p.tile0 > 0) {
+        const float2 h0 = rec[0];
+        hr = h0.x;
+        hi = h0.y;
+    }
     float dval[C::ITERS];
 #pragma unroll
     for (int it = 0; it < C::ITERS; ++it) {
         const int cc = ((lane + 32 * it) * VW) / T;
         dval[it] = (cc < nvalid && p.Dskip) ? p.Dskip[i0 + cc] : 0.f;
     }
-    const long long bo = (long long)b * N * L;
+    const long long bo = (long long)b * N * p.ld_row;
     const float* bc_src[4] = {p.B_re + bo, p.B_im ? p.B_im + bo : nullptr, p.C_re + bo, p.C_im ? p.C_im + bo : nullptr};
     const float* aux_src[AUX] = {p.u, p.dt, p.z};
+    const long long lam_b = (long long)b * p.lam_batch_stride;
     CMap<C> map;
-    map.init(lane, nvalid, N, L, p.rho, p.theta, bc_src, ch0, aux_src);
+    map.init(lane, nvalid, N, p.rho ? p.rho + lam_b : nullptr, p.theta ? p.theta + lam_b : nullptr, p.ld_lam, i0,
+             bc_src, aux_src, ch0, p.ld_row);
     for (int s = 0; s < STAGES; ++s) {
         if (s < ntiles) map.issue(smem + s * C::STAGE_FLOATS, (long long)s * T, min(T, L - s * T), lane);
         else cp_async_commit();
@@ -184,29 +206,30 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
         float* aux = bc + C::BC_ROWS * TP;
         const long long t0 = (long long)tile * T;
         const int tlen = min(T, L - (int)t0);
-        const int nq = tlen >> 2;
         cp_async_wait<STAGES - 1>();
         __syncwarp();
-        if (act && p.ckpt) {
-            float2* ck = reinterpret_cast<float2*>(p.ckpt) + (ch * N + j) * ntiles + tile;
-            *ck = make_float2(hr, hi);
-        }
+        if (rec) rec[tile] = make_float2(hr, hi);
+        // pre-pass: silu(u) replaces u, s = dt silu(u)
 #pragma unroll
         for (int it = 0; it < C::ITERS; ++it) {
             const int e0 = (lane + 32 * it) * VW;
             const int cc = e0 / T, t = e0 % T;
-            if (t < tlen) {
+            if (e0 < C::ELEMS && t < tlen) {
                 Vec<VW> u, d;
                 u.ld(aux + (cc * AUX + 0) * T + t);
                 d.ld(aux + (cc * AUX + 1) * T + t);
 #pragma unroll
-                for (int e = 0; e < VW; ++e) d.v[e] *= siluf_(u.v[e]);
+                for (int e = 0; e < VW; ++e) {
+                    u.v[e] = siluf_(u.v[e]);
+                    d.v[e] *= u.v[e];
+                }
+                u.st(aux + (cc * AUX + 0) * T + t);
                 d.st(srow + cc * T + t);
             }
         }
         __syncwarp();
 
-        for (int q = 0; q < nq; ++q) {
+        auto quad = [&](const int q) {
             const float4 s4 = ld_shared_f4(srow + c * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
             const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
@@ -214,9 +237,9 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
             const float4 ci4 = ld_shared_f4(bc + (3 * NL + j) * TP + 4 * q);
             float lr[4], li[4];
             lambda4(ld_shared_f4(st + lane * TP + 4 * q), ld_shared_f4(st + (32 + lane) * TP + 4 * q), lr, li);
-            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-            const float brv[4] = {br4.x, br4.y, br4.z, br4.w}, biv[4] = {bi4.x, bi4.y, bi4.z, bi4.w};
-            const float crv[4] = {cr4.x, cr4.y, cr4.z, cr4.w}, civ[4] = {ci4.x, ci4.y, ci4.z, ci4.w};
+            const float sv[4] = AUSSM_F4(s4);
+            const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
+            const float crv[4] = AUSSM_F4(cr4), civ[4] = AUSSM_F4(ci4);
             float pv[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -227,6 +250,12 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
                 pv[e] = act ? fmaf(crv[e], nr, -civ[e] * ni) : 0.f;
             }
             st_shared_f4(pt + lane * TP + 4 * q, make_float4(pv[0], pv[1], pv[2], pv[3]));
+        };
+        if (tlen == T) {
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) quad(q);
+        } else {
+            for (int q = 0; q < (tlen >> 2); ++q) quad(q);
         }
         __syncwarp();
 
@@ -234,23 +263,20 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
         for (int it = 0; it < C::ITERS; ++it) {
             const int e0 = (lane + 32 * it) * VW;
             const int cc = e0 / T, t = e0 % T;
-            if (t < tlen && cc < nvalid) {
-                Vec<VW> acc, u, z;
+            if (e0 < C::ELEMS && t < tlen && cc < nvalid) {
+                Vec<VW> acc, v, z;
+                acc.ld(pt + cc * NL * TP + t);
 #pragma unroll
-                for (int e = 0; e < VW; ++e) acc.v[e] = 0.f;
-#pragma unroll
-                for (int r = 0; r < NL; ++r) {
-                    Vec<VW> v;
-                    v.ld(pt + (cc * NL + r) * TP + t);
-#pragma unroll
-                    for (int e = 0; e < VW; ++e) acc.v[e] += v.v[e];
+                for (int r = 1; r < NL; ++r) {
+                    Vec<VW> a;
+                    a.ld(pt + (cc * NL + r) * TP + t);
+                    acc.add(a);
                 }
-                u.ld(aux + (cc * AUX + 0) * T + t);
+                v.ld(aux + (cc * AUX + 0) * T + t);          // silu(u), left by the pre-pass
                 z.ld(aux + (cc * AUX + 2) * T + t);
 #pragma unroll
-                for (int e = 0; e < VW; ++e)
-                    acc.v[e] = siluf_(z.v[e]) * fmaf(dval[it], siluf_(u.v[e]), acc.v[e]);
-                acc.st(p.y + (ch0 + cc) * L + t0 + t);
+                for (int e = 0; e < VW; ++e) acc.v[e] = siluf_(z.v[e]) * fmaf(dval[it], v.v[e], acc.v[e]);
+                acc.st(p.y + (ch0 + cc) * p.ld_row + t0 + t);
             }
         }
         __syncwarp();
@@ -259,6 +285,7 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
         else cp_async_commit();
     }
     cp_async_wait<0>();
+    if (rec) rec[ntiles] = make_float2(hr, hi);
 }
 
 // ---------------------------------------------------------------------------
@@ -288,14 +315,26 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
     const long long ch = ch0 + c;
     const bool has_rho = p.rho != nullptr, has_theta = p.theta != nullptr;
 
-    float* rows = smem + STAGES * C::STAGE_FLOATS;          // [CPW][2][T]: s, w
-    float* hpr = rows + CPW * C::ROWS * T;                  // [32][TP] Re h_{t-1}
-    float* hpi = hpr + 32 * TP;                             // [32][TP] Im h_{t-1}
-    float* et = hpi + 32 * TP;                              // [32][TP] Re(conj(eta) B)
-    float* pt = et + 32 * TP;                               // [32][TP] Re(C h)
+    float* rows = smem + STAGES * C::STAGE_FLOATS;          // [CPW][3][T]: s, w, d silu(u)/du
+    float* et = rows + CPW * C::ROWS * T;                   // [32][TP] Re h_{t-1}, then Re(conj(eta) B)
+    float* pt = et + 32 * TP;                               // [32][TP] Im h_{t-1}, then Re(C h)
     zero_stages<C>(smem, lane);
 
-    float er = 0.f, ei = 0.f;       // conj(lambda_{t+1}) eta_{t+1}
+    const long long rec_off = (ch * N + j) * p.states_stride + p.tile0;
+    const float2* rec = reinterpret_cast<const float2*>(p.states) + (act ? rec_off : 0);
+    const float2* grec = (p.gstates && act) ? reinterpret_cast<const float2*>(p.gstates) + rec_off : nullptr;
+    float er = 0.f, ei = 0.f;       // conj(lambda_{t+1}) eta_{t+1}: the gradient that reaches h_t from later steps
+    if (act) {
+        if (p.eta_in) {
+            const float2 e0 = reinterpret_cast<const float2*>(p.eta_in)[ch * N + j];
+            er = e0.x;
+            ei = e0.y;
+        } else if (grec) {            // last window: the gradient of the recorded final state enters here
+            const float2 g = grec[ntiles];
+            er = g.x;
+            ei = g.y;
+        }
+    }
     float dval[C::ITERS], dD_acc[C::ITERS];
 #pragma unroll
     for (int it = 0; it < C::ITERS; ++it) {
@@ -303,19 +342,19 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
         dval[it] = (cc < nvalid && p.Dskip) ? p.Dskip[i0 + cc] : 0.f;
         dD_acc[it] = 0.f;
     }
-    const long long bo = (long long)b * N * L;
+    const long long bo = (long long)b * N * p.ld_row;
     const float* bc_src[4] = {p.B_re + bo, p.B_im ? p.B_im + bo : nullptr, p.C_re + bo, p.C_im ? p.C_im + bo : nullptr};
     const float* aux_src[AUX] = {p.u, p.dt, p.z, p.gy};
+    const long long lam_b = (long long)b * p.lam_batch_stride;
     CMap<C> map;
-    map.init(lane, nvalid, N, L, p.rho, p.theta, bc_src, ch0, aux_src);
+    map.init(lane, nvalid, N, has_rho ? p.rho + lam_b : nullptr, has_theta ? p.theta + lam_b : nullptr, p.ld_lam, i0,
+             bc_src, aux_src, ch0, p.ld_row);
     for (int r = 0; r < STAGES; ++r) {
         const int tile = ntiles - 1 - r;
         if (tile >= 0) map.issue(smem + r * C::STAGE_FLOATS, (long long)tile * T, min(T, L - tile * T), lane);
         else cp_async_commit();
     }
-    const float2* ck = reinterpret_cast<const float2*>(p.ckpt) + (act ? (ch * N + j) * ntiles : 0);
-    float2 h_next = act ? ck[ntiles - 1] : make_float2(0.f, 0.f);
-    const long long own_row = (ch * N + j) * (long long)L;
+    float2 h_next = act ? rec[ntiles - 1] : make_float2(0.f, 0.f);
 
     for (int r = 0; r < ntiles; ++r) {
         const int tile = ntiles - 1 - r;
@@ -325,41 +364,49 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
         const long long t0 = (long long)tile * T;
         const int tlen = min(T, L - (int)t0);
         const int nq = tlen >> 2;
-        float hr = h_next.x, hi = h_next.y;
-        if (tile > 0 && act) h_next = ck[tile - 1];
+        float hr = h_next.x, hi = h_next.y;                 // state before the tile's first step
+        if (tile > 0 && act) h_next = rec[tile - 1];
         cp_async_wait<STAGES - 1>();
         __syncwarp();
 
+        // pre-pass: every activation once.  s = dt silu(u) and w = gy silu(z) feed the scan; silu(u) and
+        // d silu(z)/dz replace the u and z cells, d silu(u)/du gets a row of its own.
 #pragma unroll
         for (int it = 0; it < C::ITERS; ++it) {
             const int e0 = (lane + 32 * it) * VW;
             const int cc = e0 / T, t = e0 % T;
-            if (t < tlen) {
-                Vec<VW> u, d, z, g;
+            if (e0 < C::ELEMS && t < tlen) {
+                Vec<VW> u, d, z, g, gu;
                 u.ld(aux + (cc * AUX + 0) * T + t);
                 d.ld(aux + (cc * AUX + 1) * T + t);
                 z.ld(aux + (cc * AUX + 2) * T + t);
                 g.ld(aux + (cc * AUX + 3) * T + t);
 #pragma unroll
                 for (int e = 0; e < VW; ++e) {
-                    d.v[e] *= siluf_(u.v[e]);
-                    g.v[e] *= siluf_(z.v[e]);
+                    float gz;
+                    u.v[e] = silu_and_grad(u.v[e], gu.v[e]);
+                    d.v[e] *= u.v[e];
+                    g.v[e] *= silu_and_grad(z.v[e], gz);
+                    z.v[e] = gz;
                 }
-                d.st(rows + (cc * 2 + 0) * T + t);
-                g.st(rows + (cc * 2 + 1) * T + t);
+                u.st(aux + (cc * AUX + 0) * T + t);
+                z.st(aux + (cc * AUX + 2) * T + t);
+                d.st(rows + (cc * 3 + 0) * T + t);
+                g.st(rows + (cc * 3 + 1) * T + t);
+                gu.st(rows + (cc * 3 + 2) * T + t);
             }
         }
         __syncwarp();
 
-        // recompute the tile's states; keep the state before each step
-        for (int q = 0; q < nq; ++q) {
-            const float4 s4 = ld_shared_f4(rows + (c * 2 + 0) * T + 4 * q);
+        // recompute the tile's states: lambda replaces (rho, theta), the state before each step is parked
+        auto recompute = [&](const int q) {
+            const float4 s4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
             const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
             float lr[4], li[4];
             lambda4(ld_shared_f4(st + lane * TP + 4 * q), ld_shared_f4(st + (32 + lane) * TP + 4 * q), lr, li);
-            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
-            const float brv[4] = {br4.x, br4.y, br4.z, br4.w}, biv[4] = {bi4.x, bi4.y, bi4.z, bi4.w};
+            const float sv[4] = AUSSM_F4(s4);
+            const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
             float pr[4], pi[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
@@ -370,26 +417,28 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
                 hr = nr;
                 hi = ni;
             }
-            st_shared_f4(hpr + lane * TP + 4 * q, make_float4(pr[0], pr[1], pr[2], pr[3]));
-            st_shared_f4(hpi + lane * TP + 4 * q, make_float4(pi[0], pi[1], pi[2], pi[3]));
-        }
-
+            st_shared_f4(st + lane * TP + 4 * q, make_float4(lr[0], lr[1], lr[2], lr[3]));
+            st_shared_f4(st + (32 + lane) * TP + 4 * q, make_float4(li[0], li[1], li[2], li[3]));
+            st_shared_f4(et + lane * TP + 4 * q, make_float4(pr[0], pr[1], pr[2], pr[3]));
+            st_shared_f4(pt + lane * TP + 4 * q, make_float4(pi[0], pi[1], pi[2], pi[3]));
+        };
         // reverse pass
-        for (int q = nq - 1; q >= 0; --q) {
-            const float4 s4 = ld_shared_f4(rows + (c * 2 + 0) * T + 4 * q);
-            const float4 w4 = ld_shared_f4(rows + (c * 2 + 1) * T + 4 * q);
+        auto reverse = [&](const int q) {
+            const float4 s4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
+            const float4 w4 = ld_shared_f4(rows + (c * 3 + 1) * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
             const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
             const float4 cr4 = ld_shared_f4(bc + (2 * NL + j) * TP + 4 * q);
             const float4 ci4 = ld_shared_f4(bc + (3 * NL + j) * TP + 4 * q);
-            const float4 pr4 = ld_shared_f4(hpr + lane * TP + 4 * q);
-            const float4 pi4 = ld_shared_f4(hpi + lane * TP + 4 * q);
-            float lr[4], li[4];
-            lambda4(ld_shared_f4(st + lane * TP + 4 * q), ld_shared_f4(st + (32 + lane) * TP + 4 * q), lr, li);
-            const float sv[4] = {s4.x, s4.y, s4.z, s4.w}, wv[4] = {w4.x, w4.y, w4.z, w4.w};
-            const float brv[4] = {br4.x, br4.y, br4.z, br4.w}, biv[4] = {bi4.x, bi4.y, bi4.z, bi4.w};
-            const float crv[4] = {cr4.x, cr4.y, cr4.z, cr4.w}, civ[4] = {ci4.x, ci4.y, ci4.z, ci4.w};
-            const float prv[4] = {pr4.x, pr4.y, pr4.z, pr4.w}, piv[4] = {pi4.x, pi4.y, pi4.z, pi4.w};
+            const float4 lr4 = ld_shared_f4(st + lane * TP + 4 * q);
+            const float4 li4 = ld_shared_f4(st + (32 + lane) * TP + 4 * q);
+            const float4 pr4 = ld_shared_f4(et + lane * TP + 4 * q);
+            const float4 pi4 = ld_shared_f4(pt + lane * TP + 4 * q);
+            const float sv[4] = AUSSM_F4(s4), wv[4] = AUSSM_F4(w4);
+            const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
+            const float crv[4] = AUSSM_F4(cr4), civ[4] = AUSSM_F4(ci4);
+            const float lr[4] = AUSSM_F4(lr4), li[4] = AUSSM_F4(li4);
+            const float prv[4] = AUSSM_F4(pr4), piv[4] = AUSSM_F4(pi4);
             float dr[4], dth[4], E[4], P[4], gBr[4], gBi[4], gCr[4], gCi[4];
 #pragma unroll
             for (int e = 3; e >= 0; --e) {
@@ -410,8 +459,11 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
                 er = fmaf(lr[e], nr, li[e] * ni);         // conj(lambda) eta
                 ei = fmaf(lr[e], ni, -li[e] * nr);
             }
-            if (has_rho) st_shared_f4(st + lane * TP + 4 * q, make_float4(dr[0], dr[1], dr[2], dr[3]));
-            if (has_theta) st_shared_f4(st + (32 + lane) * TP + 4 * q, make_float4(dth[0], dth[1], dth[2], dth[3]));
+            // cells of a missing stream go back to zero (they are never copied again)
+            st_shared_f4(st + lane * TP + 4 * q, has_rho ? make_float4(dr[0], dr[1], dr[2], dr[3])
+                                                         : make_float4(0.f, 0.f, 0.f, 0.f));
+            st_shared_f4(st + (32 + lane) * TP + 4 * q, has_theta ? make_float4(dth[0], dth[1], dth[2], dth[3])
+                                                                  : make_float4(0.f, 0.f, 0.f, 0.f));
             st_shared_f4(et + lane * TP + 4 * q, make_float4(E[0], E[1], E[2], E[3]));
             st_shared_f4(pt + lane * TP + 4 * q, make_float4(P[0], P[1], P[2], P[3]));
 #pragma unroll
@@ -419,71 +471,93 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     gBr[e] += __shfl_xor_sync(0xffffffffu, gBr[e], off);
-                    gBi[e] += __shfl_xor_sync(0xffffffffu, gBi[e], off);
                     gCr[e] += __shfl_xor_sync(0xffffffffu, gCr[e], off);
-                    gCi[e] += __shfl_xor_sync(0xffffffffu, gCi[e], off);
+                }
+                if (p.dB_im) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) gBi[e] += __shfl_xor_sync(0xffffffffu, gBi[e], off);
+                }
+                if (p.dC_im) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) gCi[e] += __shfl_xor_sync(0xffffffffu, gCi[e], off);
                 }
             }
             if (c == 0 && j < N) {
-                const long long o = bo + (long long)j * L + t0 + 4 * q;
+                const long long o = bo + (long long)j * p.ld_row + t0 + 4 * q;
                 red_add_v4c(p.dB_re + o, gBr);
                 red_add_v4c(p.dC_re + o, gCr);
                 if (p.dB_im) red_add_v4c(p.dB_im + o, gBi);
                 if (p.dC_im) red_add_v4c(p.dC_im + o, gCi);
             }
+        };
+        if (tlen == T) {
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) recompute(q);
+#pragma unroll
+            for (int q = NQ - 1; q >= 0; --q) reverse(q);
+        } else {
+            for (int q = 0; q < nq; ++q) recompute(q);
+            for (int q = nq - 1; q >= 0; --q) reverse(q);
+        }
+        // the gradient of the recorded state at this tile's start joins the carry
+        if (grec) {
+            const float2 g = grec[tile];
+            er += g.x;
+            ei += g.y;
         }
         __syncwarp();
 
+        // post-pass: du, ddt, dz for one channel and VW steps per lane
 #pragma unroll
         for (int it = 0; it < C::ITERS; ++it) {
             const int e0 = (lane + 32 * it) * VW;
             const int cc = e0 / T, t = e0 % T;
-            if (t < tlen && cc < nvalid) {
-                Vec<VW> SE, SP, u, d, z, g, du, ddt, dz;
+            if (e0 < C::ELEMS && t < tlen && cc < nvalid) {
+                Vec<VW> SE, SP, v, d, gz, g, w, gu, du, ddt, dz;
+                SE.ld(et + cc * NL * TP + t);
+                SP.ld(pt + cc * NL * TP + t);
 #pragma unroll
-                for (int e = 0; e < VW; ++e) SE.v[e] = SP.v[e] = 0.f;
-#pragma unroll
-                for (int rr = 0; rr < NL; ++rr) {
+                for (int rr = 1; rr < NL; ++rr) {
                     Vec<VW> a, bb;
                     a.ld(et + (cc * NL + rr) * TP + t);
                     bb.ld(pt + (cc * NL + rr) * TP + t);
-#pragma unroll
-                    for (int e = 0; e < VW; ++e) { SE.v[e] += a.v[e]; SP.v[e] += bb.v[e]; }
+                    SE.add(a);
+                    SP.add(bb);
                 }
-                u.ld(aux + (cc * AUX + 0) * T + t);
+                v.ld(aux + (cc * AUX + 0) * T + t);           // silu(u)
                 d.ld(aux + (cc * AUX + 1) * T + t);
-                z.ld(aux + (cc * AUX + 2) * T + t);
+                gz.ld(aux + (cc * AUX + 2) * T + t);          // d silu(z)/dz
                 g.ld(aux + (cc * AUX + 3) * T + t);
+                w.ld(rows + (cc * 3 + 1) * T + t);            // gy silu(z)
+                gu.ld(rows + (cc * 3 + 2) * T + t);
 #pragma unroll
                 for (int e = 0; e < VW; ++e) {
-                    float gu, gz;
-                    const float v = silu_and_grad(u.v[e], gu);
-                    const float gg = silu_and_grad(z.v[e], gz);
-                    const float w = g.v[e] * gg;
-                    dz.v[e] = g.v[e] * fmaf(dval[it], v, SP.v[e]) * gz;
-                    ddt.v[e] = SE.v[e] * v;
-                    du.v[e] = fmaf(SE.v[e], d.v[e], w * dval[it]) * gu;
-                    dD_acc[it] = fmaf(w, v, dD_acc[it]);
+                    dz.v[e] = g.v[e] * fmaf(dval[it], v.v[e], SP.v[e]) * gz.v[e];
+                    ddt.v[e] = SE.v[e] * v.v[e];
+                    du.v[e] = fmaf(SE.v[e], d.v[e], w.v[e] * dval[it]) * gu.v[e];
+                    dD_acc[it] = fmaf(w.v[e], v.v[e], dD_acc[it]);
                 }
-                const long long off = (ch0 + cc) * L + t0 + t;
+                const long long off = (ch0 + cc) * p.ld_row + t0 + t;
                 du.st(p.du + off);
                 ddt.st(p.ddt + off);
                 dz.st(p.dz + off);
             }
         }
-        __syncwarp();
         // drho / dtheta leave the stage (each lane stores pieces of real rows only)
+        {
+            const int col = lane % NQ, r0 = lane / NQ;
+            constexpr int RPI = 32 / NQ;
 #pragma unroll
-        for (int i = 0; i < C::NCH_OWN; ++i) {
-            const int id = i * 32 + lane;
-            const int row = id / (T / 4), col = id % (T / 4);
-            const int w = row % 32;
-            const int rc = w / NL, rj = w % NL;
-            float* base = row < 32 ? p.drho : p.dtheta;
-            const bool on = row < 32 ? has_rho : has_theta;
-            if (on && base && rc < nvalid && rj < N && col * 4 < tlen)
-                *reinterpret_cast<float4*>(base + ((ch0 + rc) * N + rj) * (long long)L + t0 + col * 4) =
-                    ld_shared_f4(st + row * TP + col * 4);
+            for (int i = 0; i < C::NCH_OWN; ++i) {
+                const int row = i * RPI + r0;
+                const int w = row % 32;
+                const int rc = w / NL, rj = w % NL;
+                float* base = row < 32 ? p.drho : p.dtheta;
+                const bool on = row < 32 ? has_rho : has_theta;
+                if (on && base && rc < nvalid && rj < N && col * 4 < tlen)
+                    *reinterpret_cast<float4*>(base + lam_b + ((long long)(i0 + rc) * N + rj) * p.ld_lam + t0 + col * 4) =
+                        ld_shared_f4(st + row * TP + col * 4);
+            }
         }
         __syncwarp();
         const int nr = r + STAGES;
@@ -495,7 +569,7 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
         }
     }
     cp_async_wait<0>();
-    (void)own_row;
+    if (act && p.eta_out) reinterpret_cast<float2*>(p.eta_out)[ch * N + j] = make_float2(er, ei);
 
     __syncwarp();
 #pragma unroll
@@ -504,8 +578,8 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
     if (lane < nvalid) {
         float aD = 0.f;
         for (int idx = 0; idx < 32 * C::ITERS; ++idx)
-            if ((idx * VW) / T == lane) aD += et[idx];
-        p.part_D[ch0 + lane] = aD;
+            if (idx * VW < C::ELEMS && (idx * VW) / T == lane) aD += et[idx];
+        p.part_D[ch0 + lane] = aD + (p.accumulate ? p.part_D[ch0 + lane] : 0.f);
     }
 }
 

@@ -56,13 +56,16 @@ int aussm_b200_device_status(aussm_stream_t stream);
  * threads, all devices): the difference around a region counts its launches. */
 unsigned long long aussm_b200_kernel_launches(void);
 
-/* Per-thread option of the calling thread.  The only name is "window_steps":
- * steps per time window of the drop-in operators (rounded up to a multiple of
- * 64; 0 = automatic, about 2 GiB of phases per window).  It decides the layout
- * of the workspace and of a kept-phase buffer, so the size queries and the
- * forward / backward calls of one operator invocation must see the same value
- * (a kept-phase backward call refuses a buffer written under another value).
- * Returns AUSSM_EINVAL for an unknown name. */
+/* Process-wide option (one atomic word, read at the start of every operator
+ * call on whatever thread makes it - framework autograd engines run backward
+ * calls on threads of their own).  The only name is "window_steps": steps per
+ * time window of the windowed operators (rounded up to a multiple of 64; 0 =
+ * automatic, about 2 GiB of phases per window).  It decides the layout of the
+ * workspace and of a kept-phase buffer, so it is meant to be set once, before
+ * the calls that should see it: a kept-phase backward call refuses a buffer
+ * that was written under another value, and a call given a workspace sized
+ * under another value returns AUSSM_EWORKSPACE; neither computes with a wrong
+ * layout.  Returns AUSSM_EINVAL for an unknown name. */
 int aussm_b200_set_option(const char* name, int value);
 
 /* ---- scan core: the phase tensor theta is an input ----------------------
@@ -233,27 +236,57 @@ int aussm_b200_selective_scan_bwd(const float* gout, const float* u, const float
 /* ---- general complex / positive-real scan ----------------------------------
  * The recurrence of the reference's ssm_adaptive_complex and
  * ssm_adaptive_preal kernels (csrc/cuda/ssm_adaptive_complex.cu:181-744,
- * ssm_adaptive_real.cu:115-560; compiled but never registered there) on a
- * given eigenvalue:  lambda_t = exp(rho_t + i theta_t),
+ * ssm_adaptive_real.cu:115-560; compiled but never registered there):
+ *   lambda_t = exp(rho_t + i theta_t),
  *   h_t = lambda_t h_{t-1} + Bc[b][j][t] dt_t silu(u_t),
  *   y_t = silu(z_t) (Dskip_i silu(u_t) + sum_j Re(Cc[b][j][t] h_t)).
- * rho, theta, drho, dtheta: (B, D, N, L) (either input may be NULL = 0);
- * B_re, B_im, C_re, C_im and their gradients: (B, N, L) (imaginary parts may
- * be NULL = 0: positive-real variant).  L multiple of 4, N <= 32.  `ckpt`
- * (aussm_b200_scan_complex_ckpt_floats floats) receives the state at every
- * 32nd step, from which the backward pass restarts.  dB / dC use float atomics. */
-size_t aussm_b200_scan_complex_ckpt_floats(int B, int D, int N, int L);
+ * B_re, B_im, C_re, C_im and their gradients: (B, N, L) (imaginary parts may be
+ * NULL = 0: positive-real variant).  L multiple of 4, N <= 32.
+ * `states` (aussm_b200_scan_complex_states_floats floats) is the state record,
+ * this library's form of the reference's `hidden_states` output (real.cu:236,
+ * complex.cu:324): (B, D, N, L/16 + 1) complex entries, entry k = the state
+ * before step 16 k, the last entry the state after the final step.  The
+ * backward pass restarts from it; `gstates` is its upstream gradient (NULL = 0).
+ * dB / dC are summed over the channels with float atomics (as the reference's
+ * kernels do), so they are reproducible only up to rounding.
+ *
+ * Scan core: the eigenvalue exponents rho, theta (B, D, N, L) are inputs
+ * (either may be NULL = 0) and drho, dtheta outputs. */
+size_t aussm_b200_scan_complex_states_floats(int B, int D, int N, int L);
 size_t aussm_b200_scan_complex_bwd_workspace_bytes(int B, int D, int N, int L);
 int aussm_b200_scan_complex_fwd(const float* rho, const float* theta, const float* u, const float* dt,
                                 const float* z, const float* B_re, const float* B_im, const float* C_re,
-                                const float* C_im, const float* Dskip, float* y, float* ckpt, int B, int D, int N,
-                                int L, aussm_stream_t stream);
-int aussm_b200_scan_complex_bwd(const float* gy, const float* rho, const float* theta, const float* u,
-                                const float* dt, const float* z, const float* B_re, const float* B_im,
-                                const float* C_re, const float* C_im, const float* Dskip, const float* ckpt,
-                                float* drho, float* dtheta, float* du, float* ddt, float* dz, float* dB_re,
-                                float* dB_im, float* dC_re, float* dC_im, float* dD, int B, int D, int N, int L,
-                                void* workspace, size_t workspace_bytes, aussm_stream_t stream);
+                                const float* C_im, const float* Dskip, float* y, float* states, /* may be NULL */
+                                int B, int D, int N, int L, aussm_stream_t stream);
+int aussm_b200_scan_complex_bwd(const float* gy, const float* gstates, const float* rho, const float* theta,
+                                const float* u, const float* dt, const float* z, const float* B_re,
+                                const float* B_im, const float* C_re, const float* C_im, const float* Dskip,
+                                const float* states, float* drho, float* dtheta, float* du, float* ddt, float* dz,
+                                float* dB_re, float* dB_im, float* dC_re, float* dC_im, float* dD, int B, int D, int N,
+                                int L, void* workspace, size_t workspace_bytes, aussm_stream_t stream);
+
+/* Operators with the inputs of the reference's host functions:
+ * aussm_b200_complex_fwd replaces ssm_adaptive_cuda_forward_complex
+ * (ssm_adaptive_complex.cu:296-356) and, with has_theta == 0,
+ * ssm_adaptive_cuda_forward_preal (ssm_adaptive_real.cu:211-265);
+ * aussm_b200_complex_bwd replaces ssm_adaptive_cuda_backward_complex
+ * (complex.cu:662-744) / ..._backward_preal (real.cu:490-560).  The exponents
+ * rho = x_rho . u and theta = x_theta . u are computed inside, one time window
+ * at a time through `workspace` (they are never materialised for the whole
+ * sequence), and recomputed by the backward call.  x, dx: (2, D, N, D) = x_rho
+ * then x_theta when has_theta != 0, (D, N, D) = x_rho otherwise.  B and C are
+ * taken as real and imaginary parts (the reference's radius / angle pairs are
+ * converted by the host layer). */
+size_t aussm_b200_complex_workspace_bytes(int B, int D, int N, int L, int has_theta);
+int aussm_b200_complex_fwd(const float* u, const float* dt, const float* x, int has_theta, const float* B_re,
+                           const float* B_im, const float* C_re, const float* C_im, const float* Dskip,
+                           const float* z, float* y, float* states, int B, int D, int N, int L, void* workspace,
+                           size_t workspace_bytes, aussm_stream_t stream);
+int aussm_b200_complex_bwd(const float* gy, const float* gstates, const float* u, const float* dt, const float* x,
+                           int has_theta, const float* B_re, const float* B_im, const float* C_re, const float* C_im,
+                           const float* Dskip, const float* z, const float* states, float* du, float* ddt, float* dx,
+                           float* dB_re, float* dB_im, float* dC_re, float* dC_im, float* dD, float* dz, int B, int D,
+                           int N, int L, void* workspace, size_t workspace_bytes, aussm_stream_t stream);
 
 #ifdef __cplusplus
 }
