@@ -40,6 +40,12 @@ SIGNATURES = {
     "aussm_b200_selective_scan_bwd_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_selective_scan_fwd": (_I, [_P] * 8 + [_I] + [_P] * 3 + [_I] * 4 + [_P]),
     "aussm_b200_selective_scan_bwd": (_I, [_P] * 9 + [_I] + [_P] * 9 + [_I] * 4 + [_P, _Z, _P]),
+    "aussm_b200_conv_pre_fwd": (_I, [_P] * 4 + [_I] * 4 + [_P]),
+    "aussm_b200_conv_pre_bwd_workspace_bytes": (_Z, [_I] * 2),
+    "aussm_b200_conv_pre_bwd": (_I, [_P] * 6 + [_I] * 4 + [_P, _Z, _P]),
+    "aussm_b200_softplus_bias_fwd": (_I, [_P, _P, ctypes.c_float, _P] + [_I] * 3 + [_P]),
+    "aussm_b200_softplus_bias_bwd_workspace_bytes": (_Z, [_I] * 2),
+    "aussm_b200_softplus_bias_bwd": (_I, [_P, _P, ctypes.c_float, _P, _P] + [_I] * 3 + [_P, _Z, _P]),
     "aussm_b200_unitary_fwd": (_I, [_P] * 15 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_unitary_bwd": (_I, [_P] * 29 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_unitary_keep_bytes": (_Z, [_I] * 4),

@@ -288,6 +288,32 @@ int aussm_b200_complex_bwd(const float* gy, const float* gstates, const float* u
                            float* dB_re, float* dB_im, float* dC_re, float* dC_im, float* dD, float* dz, int B, int D,
                            int N, int L, void* workspace, size_t workspace_bytes, aussm_stream_t stream);
 
+/* ---- element-wise stages of the AUSSM block, in the scan's (B, D, L) layout ----
+ * What SSMauBlock does around the operator (ai-modules/wavesAI/model/aussm.py):
+ * the causal depthwise convolution with bias over time (:858-864: transpose,
+ * nn.Conv1d with padding K-1, cut back to L steps, transpose) and the step
+ * size dt = softplus(dt_proj(.) + dt_proj.bias) (:878-880, the bias entering a
+ * second time: scale = 1 adds it once to `pre`), each as one streaming pass
+ * over (B, D, L) rows with no transposing copy, and their adjoints.
+ *   u[b][i][t]  = bias[i] + sum_k w[i][k] xs[b][i][t - (K-1) + k]      w: (D, K), K <= AUSSM_MAX_CONV_TAPS
+ *   dt[b][i][t] = softplus(pre[b][i][t] + scale * bias[i])             softplus as torch's default (threshold 20)
+ * bias may be NULL.  The backward calls return the weight / bias gradients summed
+ * over batch and time in a fixed order (deterministic); dt may alias pre and
+ * dpre may alias ddt. */
+#define AUSSM_MAX_CONV_TAPS 4
+int aussm_b200_conv_pre_fwd(const float* xs, const float* w, const float* bias, float* u, int B, int D, int L, int K,
+                            aussm_stream_t stream);
+size_t aussm_b200_conv_pre_bwd_workspace_bytes(int B, int D);
+int aussm_b200_conv_pre_bwd(const float* du, const float* xs, const float* w, float* dxs, float* dw,
+                            float* dbias, /* may be NULL */
+                            int B, int D, int L, int K, void* workspace, size_t workspace_bytes, aussm_stream_t stream);
+int aussm_b200_softplus_bias_fwd(const float* pre, const float* bias, float scale, float* dt, int B, int D, int L,
+                                 aussm_stream_t stream);
+size_t aussm_b200_softplus_bias_bwd_workspace_bytes(int B, int D);
+int aussm_b200_softplus_bias_bwd(const float* ddt, const float* dt, float scale, float* dpre,
+                                 float* dbias, /* may be NULL */
+                                 int B, int D, int L, void* workspace, size_t workspace_bytes, aussm_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -41,6 +41,11 @@ def pytest_terminal_summary(terminalreporter, exitstatus, config):
     for test, name, branch, fo, mx, note in log:
         if branch != "strict":
             tr.write_line(f"  {branch:15s} {test} [{name}] outside {fo:.4%} max|err| {mx:.3e} {note}")
+    # the benchmark-size cases, one line per test: how many comparisons were strict, and the largest error
+    per_test = {}
     for test, name, branch, fo, mx, note in log:
-        if branch == "strict" and "baseline" in test:
-            tr.write_line(f"  {branch:15s} {test} [{name}] max|err| {mx:.3e}")
+        if "baseline" in test:
+            n, strict, worst = per_test.get(test, (0, 0, 0.0))
+            per_test[test] = (n + 1, strict + (branch == "strict"), max(worst, mx))
+    for test, (n, strict, worst) in per_test.items():
+        tr.write_line(f"  {test}: {strict}/{n} comparisons strict, largest |err| {worst:.3e}")

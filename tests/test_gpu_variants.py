@@ -114,7 +114,8 @@ def test_backward_operators_by_name_match_autograd_through_the_oracle(kind):
     y2, _ = fwd(*leaves)
     (y2 * gy).sum().backward()
     for g, l in zip(grads, leaves):
-        torch.testing.assert_close(l.grad, g, rtol=1e-5, atol=1e-6)
+        # dB / dC are summed with float atomics: the order, and so the last bits, differ from call to call
+        torch.testing.assert_close(l.grad, g, rtol=1e-4, atol=1e-5 * float(g.abs().max()) + 1e-7)
 
 
 @pytest.mark.parametrize("kind", ["complex", "preal"])
@@ -134,8 +135,9 @@ def test_time_windows_do_not_change_the_result(kind):
     try:
         _lib.set_option("window_steps", 64)
         lib = _lib.load()
+        # bounded workspace: it does not grow with the sequence length
         assert (lib.aussm_b200_complex_workspace_bytes(*shape, 1)
-                < lib.aussm_b200_complex_workspace_bytes(shape[0], shape[1], shape[2], 16384, 1))
+                == lib.aussm_b200_complex_workspace_bytes(shape[0], shape[1], shape[2], 16384, 1))
         six = run()
     finally:
         _lib.set_option("window_steps", 0)
