@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import ops, s6
+from . import ops, s6, stages
 from .linear import SplitLinear, split_linear
 
 __all__ = ["RMSNorm", "SSMauBlock", "MambaBlock", "ResidualBlock", "SSMTS", "SSMSequenceClassifier"]
@@ -64,21 +64,50 @@ class SSMauBlock(nn.Module):
         with torch.no_grad():
             self.xA_proj.bias.uniform_(-math.pi, math.pi)
 
+    def _operator_parameters(self):
+        # xA_proj's rows are ordered (state, channel): weight (n*d, d) -> x[i][j][r], bias -> x_bias[i][j]
+        d, n = self.d_model, self.d_state
+        x_param = self.xA_proj.weight.view(n, d, d).transpose(0, 1).contiguous() * (1.0 / math.sqrt(d))
+        x_bias = self.xA_proj.bias.view(n, d).transpose(0, 1).contiguous()
+        return x_param, x_bias
+
     def forward(self, x):
+        if x.is_cuda and x.dtype == torch.float32 and self.conv1d.kernel_size[0] <= 4:
+            return self._forward_channel_major(x)
+        # The reference's order of operations, token-major with transposes (aussm.py:849-902).  CUDA tensors
+        # take the channel-major path below; this one is what the module-glue test pins against the reference's
+        # own class on the CPU (with the oracle's scan substituted for the operator).
         b, l, d = x.shape
-        n = self.d_state
         xs, z = self.in_proj(x).split([d, d], dim=-1)
         if self.use_conv:
             xs = _causal_depthwise_conv(self.conv1d, xs)
         # the step size: the reference adds dt_proj's bias a second time before the softplus (aussm.py:878-880)
         dt = F.softplus(self.dt_proj(self.x_proj(xs)) + self.dt_proj.bias)
-        # xA_proj's rows are ordered (state, channel): weight (n*d, d) -> x[i][j][r], bias -> x_bias[i][j]
-        x_param = self.xA_proj.weight.view(n, d, d).transpose(0, 1).contiguous() * (1.0 / math.sqrt(d))
-        x_bias = self.xA_proj.bias.view(n, d).transpose(0, 1).contiguous()
+        x_param, x_bias = self._operator_parameters()
         y = ops.ssm_adaptive_interface(u=xs.transpose(1, 2).contiguous(), dt=dt.transpose(1, 2).contiguous(),
                                        x=x_param, x_bias=x_bias, B=self.B, C=self.C, D=self.D.float(),
                                        z=z.transpose(1, 2).contiguous(), unitary=True)
         return self.out_proj(y.transpose(1, 2))
+
+    def _forward_channel_major(self, x):
+        """The same block with every stage producing (b, d, l) directly: the linear layers write channel-major
+        results, the convolution with its bias and the step size (softplus with the doubled bias) are one
+        pass each, and no transposing copy exists on either side of the operator."""
+        d = self.d_model
+        w_in, b_in = self.in_proj.weight, self.in_proj.bias
+        xs = stages.project_tokens(w_in[:d], x)                      # (b, d, l)
+        z = stages.project_tokens(w_in[d:], x)
+        if b_in is not None:
+            xs = xs + b_in[:d, None]
+            z = z + b_in[d:, None]
+        u = stages.causal_conv_bias(xs, self.conv1d.weight, self.conv1d.bias) if self.use_conv else xs
+        low = stages.project_channels(self.x_proj.weight, u)         # (b, rank, l)
+        pre = stages.project_channels(self.dt_proj.weight, low)      # (b, d, l), dt_proj without its bias
+        dt = stages.softplus_bias(pre, self.dt_proj.bias, 2.0)       # the bias enters twice (aussm.py:878-880)
+        x_param, x_bias = self._operator_parameters()
+        y = ops.ssm_adaptive_interface(u=u, dt=dt, x=x_param, x_bias=x_bias, B=self.B, C=self.C, D=self.D.float(),
+                                       z=z, unitary=True)
+        return stages.project_back(self.out_proj.weight, y, self.out_proj.bias)
 
 
 class MambaBlock(nn.Module):
@@ -101,6 +130,9 @@ class MambaBlock(nn.Module):
         self.A_log._no_weight_decay = True
 
     def forward(self, x):
+        if x.is_cuda and x.dtype == torch.float32 and self.conv1d.kernel_size[0] <= 4:
+            return self._forward_channel_major(x)
+        # the reference's token-major order of operations (aussm.py:749-805); see SSMauBlock.forward
         di, n = self.d_inner, self.d_state
         xs, z = self.in_proj(x).split([di, di], dim=-1)
         xs = _causal_depthwise_conv(self.conv1d, xs)
@@ -112,6 +144,26 @@ class MambaBlock(nn.Module):
                                  z=z.transpose(1, 2).contiguous(), delta_bias=self.dt_proj.bias.float(),
                                  delta_softplus=True)
         return self.out_proj(y.transpose(1, 2))
+
+
+    def _forward_channel_major(self, x):
+        """Channel-major form of the block (see SSMauBlock._forward_channel_major)."""
+        di, n, r = self.d_inner, self.d_state, self.dt_rank
+        w_in, b_in = self.in_proj.weight, self.in_proj.bias
+        xs = stages.project_tokens(w_in[:di], x)
+        z = stages.project_tokens(w_in[di:], x)
+        if b_in is not None:
+            xs = xs + b_in[:di, None]
+            z = z + b_in[di:, None]
+        xs = stages.causal_conv_bias(xs, self.conv1d.weight, self.conv1d.bias)
+        low = stages.project_channels(self.x_proj.weight, xs)       # (b, rank + 2n, l): dt, B, C rows
+        dt = stages.project_channels(self.dt_proj.weight, low[:, :r].contiguous()) + self.dt_proj.bias[:, None]
+        # dt_proj is applied with its bias, and the bias goes in once more as delta_bias (aussm.py:786-799)
+        y = s6.selective_scan_fn(F.silu(xs), dt, (-torch.exp(self.A_log.float())).contiguous(),
+                                 low[:, r:r + n].contiguous(), low[:, r + n:].contiguous(),
+                                 self.D.float().contiguous(), z=z, delta_bias=self.dt_proj.bias.float(),
+                                 delta_softplus=True)
+        return stages.project_back(self.out_proj.weight, y, self.out_proj.bias)
 
 
 class ResidualBlock(nn.Module):

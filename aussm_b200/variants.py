@@ -39,7 +39,7 @@ def _gemm(A, a_mn, a_b, B, b_mn, b_b, C, M, N, K, batches, reduce, beta=0):
 
 
 class _Projection(torch.autograd.Function):
-    """A[b] = W @ u[b]  with W (m, d), u (b, d, l) -> (b, m, l); d and l multiples of 4."""
+    """A[b] = W @ u[b]  with W (m, d), u (b, d, l) -> (b, m, l)."""
 
     @staticmethod
     def forward(ctx, W, u):
@@ -67,19 +67,12 @@ class _Projection(torch.autograd.Function):
 
 
 def project(W: Tensor, u: Tensor) -> Tensor:
-    """``einsum('mr,brt->bmt')`` in float32 accuracy on the tensor cores (pads r and t to multiples of 4)."""
+    """``einsum('mr,brt->bmt')`` in float32 accuracy on the tensor cores."""
     W = _f32c("W", W)
     u = _f32c("u", u)
-    m, d = W.shape
-    b, d2, l = u.shape
-    if d2 != d:
+    if u.shape[1] != W.shape[1]:
         raise RuntimeError(f"projection: W is {tuple(W.shape)}, u is {tuple(u.shape)}")
-    pd, pl = (-d) % 4, (-l) % 4
-    if pd or pl:
-        W = F.pad(W, (0, pd)).contiguous()
-        u = F.pad(u, (0, pl, 0, pd)).contiguous()
-    out = _Projection.apply(W, u)
-    return out[..., :l].contiguous() if pl else out
+    return _Projection.apply(W, u)
 
 
 class _ScanComplex(torch.autograd.Function):
