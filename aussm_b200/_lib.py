@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_HERE, "libaussm_b200.so")
 _P = ctypes.c_void_p
 _I = ctypes.c_int
 _Z = ctypes.c_size_t
+_LL = ctypes.c_longlong
 
 # name -> (restype, argtypes); mirrors include/aussm_b200.h one to one
 SIGNATURES = {
@@ -22,12 +23,15 @@ SIGNATURES = {
     "aussm_b200_device_status": (_I, [_P]),
     "aussm_b200_set_option": (_I, [ctypes.c_char_p, _I]),
     "aussm_b200_scan_unitary_fwd": (_I, [_P] * 14 + [_I] * 4 + [_P]),
+    "aussm_b200_scan_unitary_fwd_workspace_bytes": (_Z, [_I] * 4),
+    "aussm_b200_scan_unitary_fwd_ws": (_I, [_P] * 14 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_scan_unitary_bwd_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_scan_unitary_bwd": (_I, [_P] * 25 + [_I] * 4 + [_P, _Z, _P]),
     "aussm_b200_scan_unitary_bwd_static": (_I, [_P] * 25 + [_I] * 4 + [_P]),
     "aussm_b200_kernel_launches": (ctypes.c_ulonglong, []),
     "aussm_b200_gemm_split3_workspace_bytes": (_Z, [_I] * 8),
     "aussm_b200_gemm_split3": (_I, [_P, _I, _I, _P, _I, _I, _P] + [_I] * 6 + [_P, _Z, _P]),
+    "aussm_b200_gemm_split3_strided": (_I, [_P, _I, _LL, _LL, _P, _I, _LL, _LL, _P, _LL, _LL] + [_I] * 6 + [_P, _Z, _P]),
     "aussm_b200_unitary_workspace_bytes": (_Z, [_I] * 4),
     "aussm_b200_scan_complex_states_floats": (_Z, [_I] * 4),
     "aussm_b200_scan_complex_bwd_workspace_bytes": (_Z, [_I] * 4),

@@ -22,12 +22,14 @@ namespace aussm {
 namespace {
 thread_local std::string t_last_error;
 std::atomic<int> g_window_steps{0};    // option "window_steps" (0 = automatic); process-wide, see the header
+std::atomic<int> g_time_split{1};      // option "time_split" (1 = cut under-filled scans into time segments)
 std::atomic<unsigned long long> g_launches{0};
 }  // namespace
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 unsigned long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
 int window_steps_option() { return g_window_steps.load(std::memory_order_relaxed); }
+int time_split_option() { return g_time_split.load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
     char buf[512];
@@ -68,7 +70,8 @@ struct Plan {
     long long rows;      // B*D*N
     int window;          // steps per window
     long long ldw;       // row pitch of the window (floats)
-    size_t off_theta, off_h, off_gh, off_part, off_proj, total;   // byte offsets
+    size_t off_theta, off_h, off_gh, off_part, off_proj, off_split, total;   // byte offsets
+    int nseg_fwd, nseg_bwd;   // time-axis split of the scans inside a window (1: none)
 };
 
 Plan make_plan(int B, int D, int N, int L, int window_steps = window_steps_option()) {
@@ -94,10 +97,21 @@ Plan make_plan(int B, int D, int N, int L, int window_steps = window_steps_optio
     off = align_up(off + (size_t)p.rows * 2 * 4, 256);
     p.off_gh = off;      // re, im
     off = align_up(off + (size_t)p.rows * 2 * 4, 256);
+    // Few channels (small batch x d_inner) leave most of the GPU idle in a scan that is sequential in time:
+    // the scans of a window are then cut into segments (only when all windows have the same length, so that
+    // the per-segment partial sums of the backward pass line up from window to window).
+    const long long nch = (long long)B * D;
+    const bool equal_windows = (L % p.window) == 0;
+    p.nseg_fwd = equal_windows ? scan_split_segments(nch, N, p.window, false) : 1;
+    p.nseg_bwd = equal_windows ? scan_split_segments(nch, N, p.window, true) : 1;
     p.off_part = off;
-    off = align_up(off + scan_bwd_partial_floats((long long)B * D, N) * 4, 256);
+    off = align_up(off + scan_bwd_partial_floats(nch * p.nseg_bwd, N) * 4, 256);
     p.off_proj = off;    // FP16 hi/lo parts of x, of the u window and of the dtheta window
     off = align_up(off + proj_scratch_bytes(B, D, (long long)D * N, p.ldw), 256);
+    p.off_split = off;
+    const size_t split_floats = std::max(p.nseg_fwd > 1 ? scan_split_fwd_scratch_floats(nch, p.nseg_fwd, N) : 0,
+                                         p.nseg_bwd > 1 ? scan_split_bwd_scratch_floats(nch, p.nseg_bwd, N) : 0);
+    off = align_up(off + split_floats * 4, 256);
     p.total = off;
     return p;
 }
@@ -187,7 +201,11 @@ int run_unitary_fwd(const OpArgs& a, const float* h0_re, const float* h0_im, flo
         sp.nch = a.B * a.D; sp.Dmod = a.D; sp.N = a.N; sp.L = tl;
         sp.ld_theta = pl.ldw;
         sp.ld_row = a.L;
-        cudaError_t e = launch_scan_unitary_fwd(sp, stream);
+        cudaError_t e;
+        if (pl.nseg_fwd > 1 && scan_split_allowed(sp))
+            e = scan_unitary_fwd_split(sp, pl.nseg_fwd, reinterpret_cast<float*>(ws + pl.off_split), stream);
+        else
+            e = launch_scan_unitary_fwd(sp, stream);
         if (e != cudaSuccess) return cuda_fail(e, "unitary scan forward launch");
     }
     return AUSSM_OK;
@@ -220,6 +238,10 @@ int aussm_b200_set_option(const char* name, int value) {
         g_window_steps.store(value > 0 ? value : 0, std::memory_order_relaxed);
         return AUSSM_OK;
     }
+    if (!strcmp(name, "time_split")) {
+        g_time_split.store(value != 0 ? 1 : 0, std::memory_order_relaxed);
+        return AUSSM_OK;
+    }
     set_error("unknown option '%s'", name);
     return AUSSM_EINVAL;
 }
@@ -247,10 +269,61 @@ int aussm_b200_scan_unitary_fwd(const float* theta, const float* u, const float*
     return AUSSM_OK;
 }
 
+size_t aussm_b200_scan_unitary_fwd_workspace_bytes(int B, int D, int N, int L) {
+    if (B <= 0 || D <= 0 || N <= 0 || L <= 0) return 0;
+    const int nseg = scan_split_segments((long long)B * D, N, L, false);
+    return nseg > 1 ? align_up(scan_split_fwd_scratch_floats((long long)B * D, nseg, N) * sizeof(float), 256) : 0;
+}
+
+int aussm_b200_scan_unitary_fwd_ws(const float* theta, const float* u, const float* dt, const float* z,
+                                   const float* B_r, const float* B_theta, const float* C_r, const float* C_theta,
+                                   const float* Dskip, const float* h0_re, const float* h0_im, float* y, float* h1_re,
+                                   float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                                   aussm_stream_t stream) {
+    const size_t need = aussm_b200_scan_unitary_fwd_workspace_bytes(B, D, N, L);
+    if (need == 0)
+        return aussm_b200_scan_unitary_fwd(theta, u, dt, z, B_r, B_theta, C_r, C_theta, Dskip, h0_re, h0_im, y, h1_re,
+                                           h1_im, B, D, N, L, stream);
+    if (!dims_ok(B, D, N, L)) return AUSSM_EINVAL;
+    if (!theta || !u || !dt || !z || !B_r || !B_theta || !C_r || !C_theta || !Dskip || !y) {
+        set_error("scan_unitary_fwd_ws: null input or output pointer");
+        return AUSSM_EINVAL;
+    }
+    if ((h0_re == nullptr) != (h0_im == nullptr) || (h1_re == nullptr) != (h1_im == nullptr)) {
+        set_error("scan_unitary_fwd_ws: real and imaginary state pointers must be given together");
+        return AUSSM_EINVAL;
+    }
+    if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15u)) {
+        set_error("scan_unitary_fwd_ws: workspace of %zu bytes (16-byte aligned) required, got %zu", need,
+                  workspace_bytes);
+        return AUSSM_EWORKSPACE;
+    }
+    ScanFwdParams p = {};
+    p.theta = theta; p.theta_bias = nullptr; p.u = u; p.dt = dt; p.z = z;
+    p.B_r = B_r; p.B_theta = B_theta; p.C_r = C_r; p.C_theta = C_theta; p.Dskip = Dskip;
+    p.h0_re = h0_re; p.h0_im = h0_im; p.y = y; p.h1_re = h1_re; p.h1_im = h1_im;
+    p.nch = B * D; p.Dmod = D; p.N = N; p.L = L; p.ld_theta = L; p.ld_row = L;
+    const int nseg = scan_split_segments((long long)B * D, N, L, false);
+    cudaError_t e = scan_split_allowed(p) ? scan_unitary_fwd_split(p, nseg, static_cast<float*>(workspace),
+                                                                   (cudaStream_t)stream)
+                                          : launch_scan_unitary_fwd(p, (cudaStream_t)stream);
+    if (e != cudaSuccess) return cuda_fail(e, "unitary scan forward launch");
+    return AUSSM_OK;
+}
+
+// backward workspace: the per-channel partial sums (one set per segment when the time axis is split), then
+// the scratch of the split
+namespace {
+int bwd_segments(int B, int D, int N, int L) { return scan_split_segments((long long)B * D, N, L, true); }
+}  // namespace
+
 size_t aussm_b200_scan_unitary_bwd_workspace_bytes(int B, int D, int N, int L) {
-    (void)L;
     if (B <= 0 || D <= 0 || N <= 0) return 0;
-    return align_up(scan_bwd_partial_floats((long long)B * D, N) * sizeof(float), 256);
+    const long long nch = (long long)B * D;
+    const int nseg = L > 0 ? bwd_segments(B, D, N, L) : 1;
+    size_t bytes = align_up(scan_bwd_partial_floats(nch * nseg, N) * sizeof(float), 256);
+    if (nseg > 1) bytes += align_up(scan_split_bwd_scratch_floats(nch, nseg, N) * sizeof(float), 256);
+    return bytes;
 }
 
 int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const float* gh1_im, const float* theta,
@@ -277,9 +350,15 @@ int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const 
         return AUSSM_EWORKSPACE;
     }
     const long long nch = (long long)B * D;
-    float* part_bc = static_cast<float*>(workspace);
-    float* part_d = part_bc + nch * N * 4;
     ScanBwdParams p = {};
+    p.theta = theta; p.dtheta = dtheta; p.u = u; p.dt = dt; p.z = z; p.gy = grad_y; p.du = du; p.ddt = ddt; p.dz = dz;
+    p.L = L; p.ld_theta = L; p.ld_dtheta = L; p.ld_row = L;
+    int nseg = bwd_segments(B, D, N, L);
+    if (nseg > 1 && !scan_split_allowed(p)) nseg = 1;
+    float* part_bc = static_cast<float*>(workspace);
+    float* part_d = part_bc + nch * nseg * N * 4;
+    float* split_scratch = reinterpret_cast<float*>(
+        static_cast<char*>(workspace) + align_up(scan_bwd_partial_floats(nch * bwd_segments(B, D, N, L), N) * sizeof(float), 256));
     p.theta = theta; p.theta_bias = nullptr; p.u = u; p.dt = dt; p.z = z; p.gy = grad_y;
     p.B_r = B_r; p.B_theta = B_theta; p.C_r = C_r; p.C_theta = C_theta; p.Dskip = Dskip;
     p.h1_re = h1_re; p.h1_im = h1_im; p.gh1_re = gh1_re; p.gh1_im = gh1_im;
@@ -287,13 +366,14 @@ int aussm_b200_scan_unitary_bwd(const float* grad_y, const float* gh1_re, const 
     p.h0_re = nullptr; p.h0_im = nullptr;
     p.part_bc = part_bc; p.part_d = part_d; p.part_rowsum = nullptr; p.accumulate = 0;
     p.nch = (int)nch; p.Dmod = D; p.N = N; p.L = L; p.ld_theta = L; p.ld_dtheta = L; p.ld_row = L;
-    cudaError_t e = launch_scan_unitary_bwd(p, (cudaStream_t)stream);
+    cudaError_t e = nseg > 1 ? scan_unitary_bwd_split(p, nseg, split_scratch, (cudaStream_t)stream)
+                             : launch_scan_unitary_bwd(p, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "unitary scan backward launch");
     ReduceParams r = {};
     r.part_bc = part_bc; r.part_d = part_d; r.part_rowsum = nullptr;
     r.B_r = B_r; r.B_theta = B_theta; r.C_r = C_r; r.C_theta = C_theta;
     r.dB_r = dB_r; r.dB_theta = dB_theta; r.dC_r = dC_r; r.dC_theta = dC_theta; r.dD = dD; r.dx_bias = nullptr;
-    r.batch = B; r.D = D; r.N = N;
+    r.batch = B; r.D = D; r.N = N; r.nseg = nseg;
     e = launch_reduce_param_grads(r, (cudaStream_t)stream);
     if (e != cudaSuccess) return cuda_fail(e, "parameter-gradient reduction launch");
     return AUSSM_OK;
@@ -320,21 +400,28 @@ size_t aussm_b200_gemm_split3_workspace_bytes(int M, int N, int K, int batches, 
     return 2 * (na + nb) * 2 + 1024;
 }
 
-int aussm_b200_gemm_split3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
-                           int b_batched, float* C, int M, int N, int K, int batches, int reduce_batches, int beta,
-                           void* workspace, size_t workspace_bytes, aussm_stream_t stream_) {
+int aussm_b200_gemm_split3_strided(const float* A, int a_mn_major, long long lda, long long a_batch_stride,
+                                   const float* Bm, int b_mn_major, long long ldb, long long b_batch_stride, float* C,
+                                   long long ldc, long long c_batch_stride, int M, int N, int K, int batches,
+                                   int reduce_batches, int beta, void* workspace, size_t workspace_bytes,
+                                   aussm_stream_t stream_) {
     if (!A || !Bm || !C || M <= 0 || N <= 0 || K <= 0 || batches <= 0) {
         set_error("gemm_split3: null pointer or non-positive size");
         return AUSSM_EINVAL;
     }
+    const int a_batched = a_batch_stride != 0, b_batched = b_batch_stride != 0;
     const size_t need = aussm_b200_gemm_split3_workspace_bytes(M, N, K, batches, a_mn_major, a_batched, b_mn_major,
                                                                b_batched);
     if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) {
         set_error("gemm_split3: workspace of %zu bytes (256-byte aligned) required, got %zu", need, workspace_bytes);
         return AUSSM_EWORKSPACE;
     }
-    cudaStream_t stream = (cudaStream_t)stream_;
     const PackedDims a = packed_dims(a_mn_major, M, K), b = packed_dims(b_mn_major, N, K);
+    if (lda < a.cols || ldb < b.cols || ldc < N) {
+        set_error("gemm_split3: a pitch is shorter than its row (lda=%lld ldb=%lld ldc=%lld)", lda, ldb, ldc);
+        return AUSSM_EINVAL;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
     const int na = a_batched ? batches : 1, nb = b_batched ? batches : 1;
     const size_t a_halves = align_up((size_t)a.rows * a.pitch * na, 128), b_halves = align_up((size_t)b.rows * b.pitch * nb, 128);
     char* w = static_cast<char*>(workspace);
@@ -343,16 +430,29 @@ int aussm_b200_gemm_split3(const float* A, int a_mn_major, int a_batched, const 
     void* b_hi = w + a_halves * 4;
     void* b_lo = w + a_halves * 4 + b_halves * 2;
     unsigned* amax = reinterpret_cast<unsigned*>(w + a_halves * 4 + b_halves * 4);   // in the spare 1 KiB
-    if (int rc = split_f16(A, a.cols, a.rows * a.cols, a_hi, a_lo, a.pitch, a.rows * a.pitch, a.rows, a.cols, na,
+    if (int rc = split_f16(A, lda, a_batch_stride, a_hi, a_lo, a.pitch, a.rows * a.pitch, a.rows, a.cols, na,
                            amax + 0, stream))
         return rc;
-    if (int rc = split_f16(Bm, b.cols, b.rows * b.cols, b_hi, b_lo, b.pitch, b.rows * b.pitch, b.rows, b.cols, nb,
+    if (int rc = split_f16(Bm, ldb, b_batch_stride, b_hi, b_lo, b.pitch, b.rows * b.pitch, b.rows, b.cols, nb,
                            amax + 1, stream))
         return rc;
     const SplitOperand sa = {a_hi, a_lo, a_mn_major, a.pitch, a_batched ? a.rows * a.pitch : 0, amax + 0};
     const SplitOperand sb = {b_hi, b_lo, b_mn_major, b.pitch, b_batched ? b.rows * b.pitch : 0, amax + 1};
-    const GemmShape shape = {M, N, K, batches, reduce_batches, beta, N, reduce_batches ? 0 : (long long)M * N};
+    const GemmShape shape = {M, N, K, batches, reduce_batches, beta, ldc, reduce_batches ? 0 : c_batch_stride};
     return gemm_split3(sa, sb, C, shape, stream);
+}
+
+int aussm_b200_gemm_split3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
+                           int b_batched, float* C, int M, int N, int K, int batches, int reduce_batches, int beta,
+                           void* workspace, size_t workspace_bytes, aussm_stream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0) {
+        set_error("gemm_split3: null pointer or non-positive size");
+        return AUSSM_EINVAL;
+    }
+    const PackedDims a = packed_dims(a_mn_major, M, K), b = packed_dims(b_mn_major, N, K);
+    return aussm_b200_gemm_split3_strided(A, a_mn_major, a.cols, a_batched ? a.rows * a.cols : 0, Bm, b_mn_major, b.cols,
+                                          b_batched ? b.rows * b.cols : 0, C, N, (long long)M * N, M, N, K, batches,
+                                          reduce_batches, beta, workspace, workspace_bytes, stream);
 }
 
 size_t aussm_b200_unitary_workspace_bytes(int B, int D, int N, int L) {
@@ -458,9 +558,16 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
     float* g_re = reinterpret_cast<float*>(ws + pl.off_gh);
     float* g_im = g_re + pl.rows;
     const long long nch = (long long)B * D;
+    // time-axis split of the backward scans: decided once per call (the partial sums of all windows share one
+    // layout); it needs the bulk-copy path, i.e. 16-byte aligned rows
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    const bool rows_aligned = (L % 4 == 0) && al16(u) && al16(dt) && al16(z) && al16(grad_y) && al16(du) && al16(ddt) &&
+                              al16(dz);
+    const int nseg_b = (pl.nseg_bwd > 1 && rows_aligned) ? pl.nseg_bwd : 1;
+    const long long nvirt = nch * nseg_b;
     float* part_bc = reinterpret_cast<float*>(ws + pl.off_part);
-    float* part_d = part_bc + nch * N * 4;
-    float* part_rowsum = part_d + nch;
+    float* part_d = part_bc + nvirt * N * 4;
+    float* part_rowsum = part_d + nvirt;
     const OpArgs a = {u, dt, x, x_bias, B_r, B_theta, C_r, C_theta, Dskip, z, B, D, N, L};
     if (keep_buf) {
         if (int rc = keep_check_layout(keep_buf, pl)) return rc;
@@ -513,7 +620,16 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
         cudaError_t em = cudaMemsetAsync(ps.amax + 2, 0, sizeof(unsigned), stream);
         if (em != cudaSuccess) return cuda_fail(em, "clearing the dtheta maximum");
         p.dtheta_amax = ps.amax + 2;
-        cudaError_t e = launch_scan_unitary_bwd(p, stream);
+        cudaError_t e;
+        if (nseg_b > 1) {
+            if (!scan_split_allowed(p)) {
+                set_error("unitary_bwd: window rows lost their 16-byte alignment (t0=%lld)", t0);
+                return AUSSM_EINVAL;
+            }
+            e = scan_unitary_bwd_split(p, nseg_b, reinterpret_cast<float*>(ws + pl.off_split), stream);
+        } else {
+            e = launch_scan_unitary_bwd(p, stream);
+        }
         if (e != cudaSuccess) return cuda_fail(e, "unitary scan backward launch");
         if (int rc = proj_adjoints(pd, theta_w, dx, du, first, ps, stream, true)) return rc;
     }
@@ -521,7 +637,7 @@ static int unitary_bwd_impl(const float* grad_y, const float* gh1_re, const floa
     r.part_bc = part_bc; r.part_d = part_d; r.part_rowsum = part_rowsum;
     r.B_r = B_r; r.B_theta = B_theta; r.C_r = C_r; r.C_theta = C_theta;
     r.dB_r = dB_r; r.dB_theta = dB_theta; r.dC_r = dC_r; r.dC_theta = dC_theta; r.dD = dD; r.dx_bias = dx_bias;
-    r.batch = B; r.D = D; r.N = N;
+    r.batch = B; r.D = D; r.N = N; r.nseg = nseg_b;
     cudaError_t e = launch_reduce_param_grads(r, stream);
     if (e != cudaSuccess) return cuda_fail(e, "parameter-gradient reduction launch");
     return AUSSM_OK;

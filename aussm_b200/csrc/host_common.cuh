@@ -15,6 +15,8 @@ unsigned long long launch_count();
 
 // Process-wide tuning value read by the drop-in operators: steps per time window (0 = automatic).
 int window_steps_option();
+// 1 (default): scans whose channels under-fill the GPU are cut into time segments; 0: never.
+int time_split_option();
 
 // Address of the device status word of the current device (nullptr on failure), and a synchronising
 // read-and-clear of it.  A kernel that gives up on a bounded wait records why there and returns.

@@ -152,6 +152,26 @@ __device__ __forceinline__ void cdiv(float ar, float ai, float kr, float ki, flo
     qi = ti * ur - tr * ui;
 }
 
+// Where the rows of a (virtual) channel start.  Without a time-axis split channel v owns rows v; with nseg
+// segments virtual channel v = ch * nseg + s owns steps [s L, (s+1) L) of the rows of channel ch.
+struct SegMap {
+    int nseg, N;
+    long long seg_len, ld_theta, ld_row;
+    __device__ __forceinline__ long long chan(long long v) const { return nseg <= 1 ? v : v / nseg; }
+    // offset (floats) of the per-channel rows (u, dt, z, y, ...)
+    __device__ __forceinline__ long long row(long long v) const {
+        return nseg <= 1 ? v * ld_row : (v / nseg) * ld_row + (v % nseg) * seg_len;
+    }
+    // offset (floats) of the theta row of state 0
+    __device__ __forceinline__ long long theta(long long v) const {
+        return nseg <= 1 ? v * N * ld_theta : (v / nseg) * N * ld_theta + (v % nseg) * seg_len;
+    }
+};
+template <class P>
+__device__ __forceinline__ SegMap seg_map(const P& p) {
+    return SegMap{p.nseg, p.N, (long long)p.L, p.ld_theta, p.ld_row};
+}
+
 // ---------------------------------------------------------------------------
 // Tile movement
 // ---------------------------------------------------------------------------
@@ -168,8 +188,9 @@ struct TileMap {
     unsigned theta_off[C::NCH_THETA];     // byte offset from the warp's first theta row (32 bits: base + offset addressing)
     const float* aux_ptr[C::NCH_AUX];     // per-channel rows (nullptr: this lane has no piece)
 
-    __device__ __forceinline__ void init(int lane, int nvalid, int N, long long ld_theta, long long ld_row,
-                                         long long ch0, const float* const* aux_src) {
+    __device__ __forceinline__ void init(int lane, int nvalid, int N, const SegMap& sm, long long ch0,
+                                         const float* const* aux_src) {
+        const long long base0 = sm.theta(ch0);
 #pragma unroll
         for (int i = 0; i < C::NCH_THETA; ++i) {
             const int id = i * 32 + lane;
@@ -177,8 +198,9 @@ struct TileMap {
             const int k = slot / 32, w = slot % 32;
             const int c = w / C::NL, j = (w % C::NL) + k * C::NL;
             const bool ok = c < nvalid && j < N;
-            const long long row = ok ? (long long)c * N + j : 0;      // missing rows shadow row 0
-            theta_off[i] = (unsigned)((row * ld_theta + col * 4) * (long long)sizeof(float));
+            // missing rows shadow the warp's first row
+            const long long row = ok ? (sm.theta(ch0 + c) - base0) + (long long)j * sm.ld_theta : 0;
+            theta_off[i] = (unsigned)((row + col * 4) * (long long)sizeof(float));
         }
 #pragma unroll
         for (int i = 0; i < C::NCH_AUX; ++i) {
@@ -188,7 +210,7 @@ struct TileMap {
             if (row < C::CPW * C::AUX) {
                 const int cc = row / C::AUX, a = row % C::AUX;
                 const long long ch = ch0 + (cc < nvalid ? cc : 0);
-                aux_ptr[i] = aux_src[a] + ch * ld_row + col * 4;
+                aux_ptr[i] = aux_src[a] + sm.row(ch) + col * 4;
             }
         }
     }
@@ -253,7 +275,9 @@ __device__ __forceinline__ void plain_load_tile(float* stage, const float* theta
 // ---------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------
-template <class C, bool ASYNC, bool NORM, bool BIAS>
+// AGG: aggregate mode of the time-axis split - no output row; besides the state, the product of the segment's
+// rotations is carried (as a unit complex number, like the state itself) and returned.
+template <class C, bool ASYNC, bool NORM, bool BIAS, bool AGG>
 __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, long long ch0, int nvalid, int lane,
                                          StateConsts (&sc)[C::SPT]) {
     constexpr int NL = C::NL, SPT = C::SPT, T = C::T, TP = C::TP, STAGES = C::STAGES, AUX = C::AUX, VW = C::VW;
@@ -261,8 +285,12 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
     const long long ch = ch0 + c;
     const int N = p.N, L = p.L;
     const int ntiles = (L + T - 1) / T;
-    const float* theta_warp = p.theta + ch0 * N * p.ld_theta;
+    const SegMap sm = seg_map(p);
+    const float* theta_warp = p.theta + sm.theta(ch0);
     const float* aux_src[AUX] = {p.u, p.dt, p.z};
+    float ar[SPT], ai[SPT];     // product of the rotations so far (aggregate mode)
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) { ar[k] = 1.f; ai[k] = 0.f; }
 
     float hr[SPT], hi[SPT];
 #pragma unroll
@@ -276,17 +304,19 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
             else { hr[k] = ar; hi[k] = ai; }
         }
     }
-    // skip weight of the channel each per-(channel, step) item of this lane belongs to
+    // skip weight and output row of the channel each per-(channel, step) item of this lane belongs to
     float dval[C::ITERS];
+    long long ybase[C::ITERS];
 #pragma unroll
     for (int it = 0; it < C::ITERS; ++it) {
         const int cc = ((lane + 32 * it) * VW) / T;
-        dval[it] = cc < nvalid ? p.Dskip[(ch0 + cc) % p.Dmod] : 0.f;
+        dval[it] = cc < nvalid ? p.Dskip[sm.chan(ch0 + cc) % p.Dmod] : 0.f;
+        ybase[it] = sm.row(ch0 + (cc < nvalid ? cc : 0));
     }
 
     TileMap<C> map;
     if (ASYNC) {
-        map.init(lane, nvalid, N, p.ld_theta, p.ld_row, ch0, aux_src);
+        map.init(lane, nvalid, N, sm, ch0, aux_src);
         for (int s = 0; s < STAGES; ++s) {
             if (s < ntiles)
                 map.issue(wsm + s * C::STAGE_FLOATS, theta_warp, (long long)s * T, min(T, L - s * T), lane);
@@ -361,11 +391,17 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
                     }
                     hr[k] = nr;
                     hi[k] = ni;
-                    pacc[e] = (k == 0) ? fmaf(sc[k].mr, nr, -sc[k].mi * ni)
-                                       : fmaf(sc[k].mr, nr, fmaf(-sc[k].mi, ni, pacc[e]));
+                    if (AGG) {
+                        const float qr = fmaf(cs[e], ar[k], -sn[e] * ai[k]);
+                        ai[k] = fmaf(cs[e], ai[k], sn[e] * ar[k]);
+                        ar[k] = qr;
+                    } else {
+                        pacc[e] = (k == 0) ? fmaf(sc[k].mr, nr, -sc[k].mi * ni)
+                                           : fmaf(sc[k].mr, nr, fmaf(-sc[k].mi, ni, pacc[e]));
+                    }
                 }
             }
-            st_shared_f4(th + lane * TP + 4 * q, make_float4(pacc[0], pacc[1], pacc[2], pacc[3]));
+            if (!AGG) st_shared_f4(th + lane * TP + 4 * q, make_float4(pacc[0], pacc[1], pacc[2], pacc[3]));
         };
         if (ASYNC && tlen == T) {
 #pragma unroll
@@ -376,7 +412,7 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
         __syncwarp();
 
         // post-pass: one lane = one channel and VW steps
-        if (p.y) {
+        if (!AGG && p.y) {
 #pragma unroll
             for (int it = 0; it < C::ITERS; ++it) {
                 const int e0 = (lane + 32 * it) * VW;
@@ -394,7 +430,7 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
                     z.ld(aux + (cc * AUX + 2) * T + t);
 #pragma unroll
                     for (int e = 0; e < VW; ++e) acc.v[e] = siluf_(z.v[e]) * fmaf(dval[it], u.v[e], acc.v[e]);
-                    float* dst = p.y + (ch0 + cc) * p.ld_row + t0 + t;
+                    float* dst = p.y + ybase[it] + t0 + t;
                     if (ASYNC) {
                         acc.st(dst);      // global pointers take the same vector stores
                     } else {
@@ -425,10 +461,15 @@ __device__ __forceinline__ void fwd_warp(const ScanFwdParams& p, float* wsm, lon
             p.h1_re[ch * N + j] = orr;
             p.h1_im[ch * N + j] = oi;
         }
+        if (AGG && sc[k].act && p.agg_re) {
+            const int j = jl + k * NL;
+            p.agg_re[ch * N + j] = ar[k];
+            p.agg_im[ch * N + j] = ai[k];
+        }
     }
 }
 
-template <class C, bool ASYNC, bool BIAS>
+template <class C, bool ASYNC, bool BIAS, bool AGG>
 __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const ScanFwdParams p) {
     extern __shared__ __align__(128) float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -437,7 +478,7 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const S
     const int nvalid = (int)min((long long)C::CPW, (long long)p.nch - ch0);
     float* wsm = smem + (size_t)warp * C::WARP_FLOATS;
     const int c = lane / C::NL, jl = lane % C::NL;
-    const int i = (int)((ch0 + min(c, nvalid - 1)) % p.Dmod);
+    const int i = (int)(seg_map(p).chan(ch0 + min(c, nvalid - 1)) % p.Dmod);
     StateConsts sc[C::SPT];
     bool ok = true;
 #pragma unroll
@@ -454,9 +495,9 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_fwd_kernel(const S
             float a, b;
             normalise_consts(sc[k], a, b);
         }
-        fwd_warp<C, ASYNC, true, BIAS>(p, wsm, ch0, nvalid, lane, sc);
+        fwd_warp<C, ASYNC, true, BIAS, AGG>(p, wsm, ch0, nvalid, lane, sc);
     } else {
-        fwd_warp<C, ASYNC, false, BIAS>(p, wsm, ch0, nvalid, lane, sc);
+        fwd_warp<C, ASYNC, false, BIAS, AGG>(p, wsm, ch0, nvalid, lane, sc);
     }
 }
 
@@ -473,8 +514,9 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
     const long long ch = ch0 + c;
     const int N = p.N, L = p.L;
     const int ntiles = (L + T - 1) / T;
-    const float* theta_warp = p.theta + ch0 * N * p.ld_theta;
-    float* dtheta_warp = p.dtheta + ch0 * N * p.ld_theta;       // launcher guarantees equal pitches
+    const SegMap sm = seg_map(p);
+    const float* theta_warp = p.theta + sm.theta(ch0);
+    float* dtheta_warp = p.dtheta + sm.theta(ch0);              // launcher guarantees equal pitches
 
     float* scratch = wsm + STAGES * C::STAGE_FLOATS;
     float* pt = scratch;                    // [32][TSP] projections, summed over a thread's states
@@ -510,18 +552,20 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
         }
     }
     float dval[C::ITERS], dacc[C::ITERS];
+    long long obase[C::ITERS];
 #pragma unroll
     for (int it = 0; it < C::ITERS; ++it) {
         const int cc = ((lane + 32 * it) * VW) / TS;
-        dval[it] = cc < nvalid ? p.Dskip[(ch0 + cc) % p.Dmod] : 0.f;
+        dval[it] = cc < nvalid ? p.Dskip[sm.chan(ch0 + cc) % p.Dmod] : 0.f;
         dacc[it] = 0.f;
+        obase[it] = sm.row(ch0 + (cc < nvalid ? cc : 0));
     }
     const float* aux_src[AUX] = {p.u, p.dt, p.z, p.gy};
 
     // r counts tiles in processing order (last tile first)
     TileMap<C> map;
     if (ASYNC) {
-        map.init(lane, nvalid, N, p.ld_theta, p.ld_row, ch0, aux_src);
+        map.init(lane, nvalid, N, sm, ch0, aux_src);
         for (int r = 0; r < STAGES; ++r) {
             const int tile = ntiles - 1 - r;
             if (tile >= 0)
@@ -678,7 +722,7 @@ __device__ __forceinline__ void bwd_warp(const ScanBwdParams& p, float* wsm, lon
                         du.v[e] = fmaf(E.v[e], d.v[e], w.v[e] * dv) * gu.v[e];
                         if (ASYNC || t + e < slen) dacc[it] = fmaf(w.v[e], v.v[e], dacc[it]);
                     }
-                    const long long off = (ch0 + cc) * p.ld_row + t0 + o;
+                    const long long off = obase[it] + t0 + o;
                     if (ASYNC) {
                         du.st(p.du + off);
                         ddt.st(p.ddt + off);
@@ -803,7 +847,7 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_bwd_kernel(const S
     const int nvalid = (int)min((long long)C::CPW, (long long)p.nch - ch0);
     float* wsm = smem + (size_t)warp * C::WARP_FLOATS;
     const int c = lane / C::NL, jl = lane % C::NL;
-    const int i = (int)((ch0 + min(c, nvalid - 1)) % p.Dmod);
+    const int i = (int)(seg_map(p).chan(ch0 + min(c, nvalid - 1)) % p.Dmod);
     StateConsts sc[C::SPT];
     float ccr[C::SPT], cci[C::SPT];
     bool ok = true;
@@ -827,13 +871,186 @@ __global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_bwd_kernel(const S
 }
 
 // ---------------------------------------------------------------------------
+// Adjoint-only reverse pass (time-axis split): for every (virtual) channel the gradient that the segment's own
+// grad_y sends to the state before the segment, from a zero gradient after it:
+//     e <- conj(lambda_t) (e + conj(Cc) w_t),  t = L-1 .. 0,   w_t = gy_t silu(z_t)
+// (general representation, no state regeneration, nothing else produced).
+// ---------------------------------------------------------------------------
+template <class C, bool BIAS>
+__global__ void __launch_bounds__(C::WARPS * 32) scan_unitary_eta_kernel(const ScanBwdParams p) {
+    constexpr int NL = C::NL, SPT = C::SPT, T = C::T, TP = C::TP, STAGES = C::STAGES, AUX = C::AUX, VW = C::VW;
+    extern __shared__ __align__(128) float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long ch0 = ((long long)blockIdx.x * C::WARPS + warp) * C::CPW;
+    if (ch0 >= p.nch) return;
+    const int nvalid = (int)min((long long)C::CPW, (long long)p.nch - ch0);
+    float* wsm = smem + (size_t)warp * C::WARP_FLOATS;
+    const int c = lane / NL, jl = lane % NL;
+    const SegMap sm = seg_map(p);
+    const int i = (int)(sm.chan(ch0 + min(c, nvalid - 1)) % p.Dmod);
+    const long long ch = ch0 + c;
+    const int N = p.N, L = p.L;
+    const int ntiles = (L + T - 1) / T;
+    StateConsts sc[SPT];
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) {
+        bool okk;
+        load_state_consts(sc[k], c < nvalid && jl + k * NL < N, jl + k * NL, i, N, p.B_r, p.B_theta, p.C_r, p.C_theta,
+                          BIAS ? p.theta_bias : nullptr, okk);      // mr, mi hold Cc
+    }
+    const float* theta_warp = p.theta + sm.theta(ch0);
+    const float* aux_src[AUX] = {p.u, p.dt, p.z, p.gy};
+    float er[SPT], ei[SPT];
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) er[k] = ei[k] = 0.f;
+    TileMap<C> map;
+    map.init(lane, nvalid, N, sm, ch0, aux_src);
+    for (int r = 0; r < STAGES; ++r) {
+        const int tile = ntiles - 1 - r;
+        if (tile >= 0) map.issue(wsm + r * C::STAGE_FLOATS, theta_warp, (long long)tile * T, min(T, L - tile * T), lane);
+        else cp_async_commit();
+    }
+    for (int r = 0; r < ntiles; ++r) {
+        const int tile = ntiles - 1 - r;
+        float* th = wsm + (r % STAGES) * C::STAGE_FLOATS;
+        float* aux = th + C::NROWS * TP;
+        const int tlen = min(T, L - tile * T);
+        cp_async_wait<STAGES - 1>();
+        __syncwarp();
+        // pre-pass: w = gy silu(z) replaces gy
+#pragma unroll
+        for (int it = 0; it < C::ITERS; ++it) {
+            const int e0 = (lane + 32 * it) * VW;
+            const int cc = e0 / T, t = e0 % T;
+            if (t < tlen) {
+                Vec<VW> z, g;
+                z.ld(aux + (cc * AUX + 2) * T + t);
+                g.ld(aux + (cc * AUX + 3) * T + t);
+#pragma unroll
+                for (int e = 0; e < VW; ++e) g.v[e] *= siluf_(z.v[e]);
+                g.st(aux + (cc * AUX + 3) * T + t);
+            }
+        }
+        __syncwarp();
+        const float* wrow = aux + (c * AUX + 3) * T;
+        for (int q = (tlen >> 2) - 1; q >= 0; --q) {
+            const float4 w4 = ld_shared_f4(wrow + 4 * q);
+            const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+            for (int k = 0; k < SPT; ++k) {
+                const float4 t4 = ld_shared_f4(th + (k * 32 + lane) * TP + 4 * q);
+                float tv[4] = {t4.x, t4.y, t4.z, t4.w};
+                if (BIAS) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) tv[e] += sc[k].bias;
+                }
+                float sn[4], cs[4];
+                sincos4(tv, sn, cs);
+#pragma unroll
+                for (int e = 3; e >= 0; --e) {
+                    const float nr = fmaf(sc[k].mr, wv[e], er[k]);
+                    const float ni = fmaf(-sc[k].mi, wv[e], ei[k]);
+                    er[k] = fmaf(cs[e], nr, sn[e] * ni);
+                    ei[k] = fmaf(cs[e], ni, -sn[e] * nr);
+                }
+            }
+        }
+        __syncwarp();
+        const int nr2 = r + STAGES;
+        if (nr2 < ntiles) {
+            const int nt = ntiles - 1 - nr2;
+            map.issue(th, theta_warp, (long long)nt * T, min(T, L - nt * T), lane);
+        } else {
+            cp_async_commit();
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int k = 0; k < SPT; ++k) {
+        if (sc[k].act) {
+            const long long o = ch * N + jl + k * NL;
+            p.dh0_re[o] = er[k];
+            p.dh0_im[o] = ei[k];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Segment chains of the time-axis split: one thread per (channel, state) walks the nseg segments.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) segment_states_fwd_kernel(const float* e_re, const float* e_im,
+                                                                 const float* a_re, const float* a_im,
+                                                                 const float* start_re, const float* start_im,
+                                                                 float* before_re, float* before_im, float* final_re,
+                                                                 float* final_im, long long total, int nseg, int N) {
+    const long long id = (long long)blockIdx.x * 256 + threadIdx.x;      // ch * N + j
+    if (id >= total) return;
+    const long long ch = id / N, j = id % N;
+    float cr = start_re ? start_re[id] : 0.f, ci = start_im ? start_im[id] : 0.f;
+    for (int s = 0; s < nseg; ++s) {
+        const long long o = (ch * nseg + s) * N + j;
+        before_re[o] = cr;
+        before_im[o] = ci;
+        const float ar = a_re[o], ai = a_im[o];
+        const float nr = fmaf(ar, cr, fmaf(-ai, ci, e_re[o]));
+        ci = fmaf(ar, ci, fmaf(ai, cr, e_im[o]));
+        cr = nr;
+    }
+    if (final_re) { final_re[id] = cr; final_im[id] = ci; }
+}
+
+__global__ void __launch_bounds__(256) segment_states_bwd_kernel(const float* e_re, const float* e_im,
+                                                                 const float* a_re, const float* a_im,
+                                                                 const float* final_re, const float* final_im,
+                                                                 float* after_re, float* after_im, float* first_re,
+                                                                 float* first_im, long long total, int nseg, int N) {
+    const long long id = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (id >= total) return;
+    const long long ch = id / N, j = id % N;
+    float cr = final_re[id], ci = final_im[id];
+    for (int s = nseg - 1; s >= 0; --s) {
+        const long long o = (ch * nseg + s) * N + j;
+        after_re[o] = cr;
+        after_im[o] = ci;
+        // the rotations have modulus one: the state before the segment is conj(a) (c - e)
+        const float dr = cr - e_re[o], di = ci - e_im[o];
+        const float ar = a_re[o], ai = a_im[o];
+        cr = fmaf(ar, dr, ai * di);
+        ci = fmaf(ar, di, -ai * dr);
+    }
+    if (first_re) { first_re[id] = cr; first_im[id] = ci; }
+}
+
+__global__ void __launch_bounds__(256) segment_adjoints_kernel(const float* l_re, const float* l_im, const float* a_re,
+                                                               const float* a_im, const float* last_re,
+                                                               const float* last_im, float* after_re, float* after_im,
+                                                               float* first_re, float* first_im, long long total,
+                                                               int nseg, int N) {
+    const long long id = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (id >= total) return;
+    const long long ch = id / N, j = id % N;
+    float gr = last_re ? last_re[id] : 0.f, gi = last_im ? last_im[id] : 0.f;
+    for (int s = nseg - 1; s >= 0; --s) {
+        const long long o = (ch * nseg + s) * N + j;
+        after_re[o] = gr;
+        after_im[o] = gi;
+        const float ar = a_re[o], ai = a_im[o];
+        const float nr = fmaf(ar, gr, fmaf(ai, gi, l_re[o]));          // l + conj(a) g
+        gi = fmaf(ar, gi, fmaf(-ai, gr, l_im[o]));
+        gr = nr;
+    }
+    if (first_re) { first_re[id] = gr; first_im[id] = gi; }
+}
+
+// ---------------------------------------------------------------------------
 // Second stage: fixed-order sums of the per-channel partials (deterministic)
 // and the polar chain rule  dr = Re(conj(G) e^{i phi}),  dphi = -Im(conj(G) w).
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) reduce_param_grads_kernel(const ReduceParams p) {
     __shared__ float4 red[256];
     const int tid = threadIdx.x;
-    const long long nch = (long long)p.batch * p.D;
+    const int nseg = p.nseg > 1 ? p.nseg : 1;               // partial arrays: nseg entries per channel
+    const long long nch = (long long)p.batch * p.D * nseg;
     if (blockIdx.x < p.N) {
         const int j = blockIdx.x;
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -867,12 +1084,16 @@ __global__ void __launch_bounds__(256) reduce_param_grads_kernel(const ReducePar
     const long long o = (long long)(blockIdx.x - p.N) * 256 + tid;
     if (o < p.D) {
         float acc = 0.f;
-        for (int b = 0; b < p.batch; ++b) acc += p.part_d[(long long)b * p.D + o];
+        for (int b = 0; b < p.batch; ++b)
+            for (int sg = 0; sg < nseg; ++sg) acc += p.part_d[((long long)b * p.D + o) * nseg + sg];
         p.dD[o] = acc;
     } else if (p.dx_bias && o - p.D < (long long)p.D * p.N) {
         const long long e = o - p.D;
+        const long long i = e / p.N, j = e % p.N;
         float acc = 0.f;
-        for (int b = 0; b < p.batch; ++b) acc += p.part_rowsum[(long long)b * p.D * p.N + e];
+        for (int b = 0; b < p.batch; ++b)
+            for (int sg = 0; sg < nseg; ++sg)
+                acc += p.part_rowsum[(((long long)b * p.D + i) * nseg + sg) * p.N + j];
         p.dx_bias[e] = acc;
     }
 }
@@ -882,9 +1103,9 @@ __global__ void __launch_bounds__(256) reduce_param_grads_kernel(const ReducePar
 // ---------------------------------------------------------------------------
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <class C, bool ASYNC, bool BIAS>
+template <class C, bool ASYNC, bool BIAS, bool AGG>
 cudaError_t launch_fwd_cfg(const ScanFwdParams& p, cudaStream_t stream) {
-    auto kern = scan_unitary_fwd_kernel<C, ASYNC, BIAS>;
+    auto kern = scan_unitary_fwd_kernel<C, ASYNC, BIAS, AGG>;
     const size_t smem = C::SMEM_BYTES;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -913,14 +1134,32 @@ cudaError_t launch_bwd_cfg(const ScanBwdParams& p, cudaStream_t stream) {
 template <class C>
 cudaError_t launch_fwd_sel(const ScanFwdParams& p, bool async, cudaStream_t s) {
     const bool bias = p.theta_bias != nullptr;
-    if (!async) return launch_fwd_cfg<C, false, true>(p, s);
-    return bias ? launch_fwd_cfg<C, true, true>(p, s) : launch_fwd_cfg<C, true, false>(p, s);
+    if (!async) return p.nseg > 1 || p.agg_re ? cudaErrorInvalidValue : launch_fwd_cfg<C, false, true, false>(p, s);
+    if (p.agg_re != nullptr && p.y == nullptr)
+        return bias ? launch_fwd_cfg<C, true, true, true>(p, s) : launch_fwd_cfg<C, true, false, true>(p, s);
+    return bias ? launch_fwd_cfg<C, true, true, false>(p, s) : launch_fwd_cfg<C, true, false, false>(p, s);
 }
+
+template <class C, bool BIAS>
+cudaError_t launch_eta_cfg(const ScanBwdParams& p, cudaStream_t stream) {
+    auto kern = scan_unitary_eta_kernel<C, BIAS>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    const long long tasks = ((long long)p.nch + C::CPW - 1) / C::CPW;
+    const long long blocks = (tasks + C::WARPS - 1) / C::WARPS;
+    kern<<<(unsigned)blocks, C::WARPS * 32, C::SMEM_BYTES, stream>>>(p);
+    count_launch();
+    return cudaGetLastError();
+}
+
+// the adjoint-only pass stages (u, dt, z, gy) like the backward kernel but keeps no column-sum tiles
+template <int NL, int SPT, int T, int STAGES, int WARPS>
+using EtaCfg = Cfg<NL, SPT, T, T, STAGES, WARPS, 4, false>;
 
 template <class C>
 cudaError_t launch_bwd_sel(const ScanBwdParams& p, bool async, cudaStream_t s) {
     const bool bias = p.theta_bias != nullptr || p.part_rowsum != nullptr;
-    if (!async) return launch_bwd_cfg<C, false, true>(p, s);
+    if (!async) return p.nseg > 1 ? cudaErrorInvalidValue : launch_bwd_cfg<C, false, true>(p, s);
     return bias ? launch_bwd_cfg<C, true, true>(p, s) : launch_bwd_cfg<C, true, false>(p, s);
 }
 
@@ -960,6 +1199,19 @@ cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p_, cudaStream_t stream
                        aligned16(p.gy) && aligned16(p.du) && aligned16(p.ddt) && aligned16(p.dz) &&
                        offsets_fit(p.ld_theta, 128);
     const int N = p.N;
+    if (p.eta_only) {
+        if (!async || !p.dh0_re) return cudaErrorInvalidValue;
+        const bool bias = p.theta_bias != nullptr;
+#define AUSSM_ETA(...) (bias ? launch_eta_cfg<__VA_ARGS__, true>(p, stream) : launch_eta_cfg<__VA_ARGS__, false>(p, stream))
+        if (N <= 4) return AUSSM_ETA(EtaCfg<4, 1, 32, 2, 4>);
+        if (N <= 8) return AUSSM_ETA(EtaCfg<8, 1, 32, 2, 4>);
+        if (N <= 16) return AUSSM_ETA(EtaCfg<16, 1, 32, 2, 4>);
+        if (N <= 32) return AUSSM_ETA(EtaCfg<32, 1, 32, 2, 4>);
+        if (N <= 64) return AUSSM_ETA(EtaCfg<32, 2, 32, 2, 4>);
+        if (N <= 128) return AUSSM_ETA(EtaCfg<32, 4, 32, 2, 2>);
+#undef AUSSM_ETA
+        return cudaErrorInvalidValue;
+    }
     if (N <= 4) return launch_bwd_sel<BwdCfg<4, 1, 32, 32, 2, 2>>(p, async, stream);
     if (N <= 8) return launch_bwd_sel<BwdCfg<8, 1, 32, 32, 2, 2>>(p, async, stream);
     // one-warp blocks: a finished warp is replaced at once (measured 9.55 ms against 10.2 ms with two-warp blocks)
@@ -968,6 +1220,128 @@ cudaError_t launch_scan_unitary_bwd(const ScanBwdParams& p_, cudaStream_t stream
     if (N <= 64) return launch_bwd_sel<BwdCfg<32, 2, 32, 32, 2, 2>>(p, async, stream);
     if (N <= 128) return launch_bwd_sel<BwdCfg<32, 4, 32, 32, 2, 2>>(p, async, stream);
     return cudaErrorInvalidValue;
+}
+
+int scan_split_segments(long long nch, int N, int L, bool bwd) {
+    if (nch <= 0 || L <= 0 || N <= 0 || N > 128 || !time_split_option()) return 1;
+    // warps the launch has and warps the GPU holds (148 SMs; 20 resident forward warps per SM, 10 backward:
+    // shared memory limits both)
+    const int nl = N <= 4 ? 4 : N <= 8 ? 8 : N <= 16 ? 16 : 32;
+    const long long warps = (nch + (32 / nl) - 1) / (32 / nl);
+    const long long slots = 148LL * (bwd ? 10 : 20);
+    // a split doubles the work (an aggregate pass before the real one), and an SM with a third of its warps
+    // resident is already more than half busy, so it pays only when the launch fills less than a quarter
+    if (warps * 4 > slots) return 1;
+    int best = 1;
+    for (int s = 2; s <= 64; s *= 2) {
+        if (L % s != 0 || (L / s) % 32 != 0 || L / s < 256) break;
+        best = s;
+        if (warps * s >= slots) break;
+    }
+    return best;
+}
+
+namespace {
+unsigned seg_blocks(long long total) { return (unsigned)((total + 255) / 256); }
+}  // namespace
+
+cudaError_t launch_segment_states_fwd(const float* e_re, const float* e_im, const float* a_re, const float* a_im,
+                                      const float* start_re, const float* start_im, float* before_re,
+                                      float* before_im, float* final_re, float* final_im, long long nch, int nseg,
+                                      int N, cudaStream_t stream) {
+    const long long total = nch * N;
+    segment_states_fwd_kernel<<<seg_blocks(total), 256, 0, stream>>>(e_re, e_im, a_re, a_im, start_re, start_im,
+                                                                      before_re, before_im, final_re, final_im, total,
+                                                                      nseg, N);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_segment_states_bwd(const float* e_re, const float* e_im, const float* a_re, const float* a_im,
+                                      const float* final_re, const float* final_im, float* after_re, float* after_im,
+                                      float* first_re, float* first_im, long long nch, int nseg, int N,
+                                      cudaStream_t stream) {
+    const long long total = nch * N;
+    segment_states_bwd_kernel<<<seg_blocks(total), 256, 0, stream>>>(e_re, e_im, a_re, a_im, final_re, final_im,
+                                                                      after_re, after_im, first_re, first_im, total,
+                                                                      nseg, N);
+    count_launch();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_segment_adjoints(const float* l_re, const float* l_im, const float* a_re, const float* a_im,
+                                    const float* last_re, const float* last_im, float* after_re, float* after_im,
+                                    float* first_re, float* first_im, long long nch, int nseg, int N,
+                                    cudaStream_t stream) {
+    const long long total = nch * N;
+    segment_adjoints_kernel<<<seg_blocks(total), 256, 0, stream>>>(l_re, l_im, a_re, a_im, last_re, last_im, after_re,
+                                                                    after_im, first_re, first_im, total, nseg, N);
+    count_launch();
+    return cudaGetLastError();
+}
+
+bool scan_split_allowed(const ScanFwdParams& p) {
+    return (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) && aligned16(p.theta) && aligned16(p.u) &&
+           aligned16(p.dt) && aligned16(p.z) && (p.y == nullptr || aligned16(p.y)) && offsets_fit(p.ld_theta, 128);
+}
+
+bool scan_split_allowed(const ScanBwdParams& p) {
+    return (p.L % 4 == 0) && (p.ld_theta % 4 == 0) && (p.ld_row % 4 == 0) && p.ld_dtheta == p.ld_theta &&
+           aligned16(p.theta) && aligned16(p.dtheta) && aligned16(p.u) && aligned16(p.dt) && aligned16(p.z) &&
+           aligned16(p.gy) && aligned16(p.du) && aligned16(p.ddt) && aligned16(p.dz) && offsets_fit(p.ld_theta, 128);
+}
+
+// Forward with the time axis cut into nseg segments per channel: (A) every segment from a zero state, without
+// output: its end state e and the product a of its rotations; (B) the chain c_{s+1} = e_s + a_s c_s gives the
+// state before every segment; (C) the real pass, every segment from its true initial state.
+cudaError_t scan_unitary_fwd_split(const ScanFwdParams& p, int nseg, float* scratch, cudaStream_t stream) {
+    const long long V = (long long)p.nch * nseg, VN = V * p.N;
+    float *e_re = scratch, *e_im = e_re + VN, *a_re = e_im + VN, *a_im = a_re + VN, *b_re = a_im + VN,
+          *b_im = b_re + VN;
+    ScanFwdParams q = p;
+    q.nch = (int)V; q.L = p.L / nseg; q.nseg = nseg;
+    q.y = nullptr; q.h0_re = q.h0_im = nullptr; q.h1_re = e_re; q.h1_im = e_im; q.agg_re = a_re; q.agg_im = a_im;
+    cudaError_t err = launch_scan_unitary_fwd(q, stream);
+    if (err != cudaSuccess) return err;
+    err = launch_segment_states_fwd(e_re, e_im, a_re, a_im, p.h0_re, p.h0_im, b_re, b_im, p.h1_re, p.h1_im, p.nch, nseg,
+                                    p.N, stream);
+    if (err != cudaSuccess) return err;
+    if (!p.y) return cudaSuccess;                       // state-only call: the chain already gave the final state
+    q.y = p.y; q.h0_re = b_re; q.h0_im = b_im; q.h1_re = q.h1_im = nullptr; q.agg_re = q.agg_im = nullptr;
+    return launch_scan_unitary_fwd(q, stream);
+}
+
+// Backward with the same cut: (A) the forward aggregates again; (B) the state after every segment, walking
+// back from the final state (the rotations are invertible); (C) every segment's own contribution to the
+// gradient of the state before it; (D) the chain g_s = l_s + conj(a_s) g_{s+1} gives the gradient after every
+// segment; (E) the real backward pass, every segment with its true end state and incoming gradient.
+cudaError_t scan_unitary_bwd_split(const ScanBwdParams& p, int nseg, float* scratch, cudaStream_t stream) {
+    const long long V = (long long)p.nch * nseg, VN = V * p.N;
+    float *e_re = scratch, *e_im = e_re + VN, *a_re = e_im + VN, *a_im = a_re + VN, *s_re = a_im + VN,
+          *s_im = s_re + VN, *l_re = s_im + VN, *l_im = l_re + VN, *g_re = l_im + VN, *g_im = g_re + VN;
+    ScanFwdParams f = {};
+    f.theta = p.theta; f.theta_bias = p.theta_bias; f.u = p.u; f.dt = p.dt; f.z = p.z;
+    f.B_r = p.B_r; f.B_theta = p.B_theta; f.C_r = p.C_r; f.C_theta = p.C_theta; f.Dskip = p.Dskip;
+    f.h1_re = e_re; f.h1_im = e_im; f.agg_re = a_re; f.agg_im = a_im;
+    f.nch = (int)V; f.Dmod = p.Dmod; f.N = p.N; f.L = p.L / nseg; f.ld_theta = p.ld_theta; f.ld_row = p.ld_row;
+    f.nseg = nseg;
+    cudaError_t err = launch_scan_unitary_fwd(f, stream);
+    if (err != cudaSuccess) return err;
+    err = launch_segment_states_bwd(e_re, e_im, a_re, a_im, p.h1_re, p.h1_im, s_re, s_im, p.h0_re, p.h0_im, p.nch, nseg,
+                                    p.N, stream);
+    if (err != cudaSuccess) return err;
+    ScanBwdParams q = p;
+    q.nch = (int)V; q.L = p.L / nseg; q.nseg = nseg;
+    q.eta_only = 1; q.dh0_re = l_re; q.dh0_im = l_im;
+    err = launch_scan_unitary_bwd(q, stream);
+    if (err != cudaSuccess) return err;
+    err = launch_segment_adjoints(l_re, l_im, a_re, a_im, p.gh1_re, p.gh1_im, g_re, g_im, p.dh0_re, p.dh0_im, p.nch,
+                                  nseg, p.N, stream);
+    if (err != cudaSuccess) return err;
+    q.eta_only = 0;
+    q.h1_re = s_re; q.h1_im = s_im; q.gh1_re = g_re; q.gh1_im = g_im;
+    q.dh0_re = q.dh0_im = nullptr; q.h0_re = q.h0_im = nullptr;
+    return launch_scan_unitary_bwd(q, stream);
 }
 
 cudaError_t launch_reduce_param_grads(const ReduceParams& p, cudaStream_t stream) {

@@ -350,10 +350,15 @@ class _ScanUnitary(torch.autograd.Function):
         y = torch.empty_like(u)
         h_re = torch.empty((b, d, n), device=u.device, dtype=torch.float32)
         h_im = torch.empty_like(h_re)
+        lib = _lib.load()
         with torch.cuda.device(u.device):
-            rc = _lib.load().aussm_b200_scan_unitary_fwd(
+            # the workspace is non-empty only when the launch is cut into time segments (few channels)
+            nbytes = lib.aussm_b200_scan_unitary_fwd_workspace_bytes(b, d, n, l)
+            ws = _workspace(nbytes, u.device) if nbytes else None
+            rc = lib.aussm_b200_scan_unitary_fwd_ws(
                 _ptr(theta), _ptr(u), _ptr(dt), _ptr(z), _ptr(B_r), _ptr(B_theta), _ptr(C_r), _ptr(C_theta), _ptr(D),
-                _ptr(h0_re), _ptr(h0_im), _ptr(y), _ptr(h_re), _ptr(h_im), b, d, n, l, _stream(u))
+                _ptr(h0_re), _ptr(h0_im), _ptr(y), _ptr(h_re), _ptr(h_im), b, d, n, l, _ptr(ws),
+                0 if ws is None else ws.numel(), _stream(u))
         _lib.check(rc, "scan_unitary forward")
         ctx.save_for_backward(theta, u, dt, z, B_r, B_theta, C_r, C_theta, D, h_re, h_im)
         ctx.has_h0 = h0_re is not None

@@ -119,6 +119,34 @@ def _big(flop: float, *dims: int) -> bool:
     return flop >= MIN_FLOP
 
 
+def _weight_grad(A: Tensor, a_mn: int, B: Tensor, b_mn: int, m: int, k: int, l: int, b: int) -> Tensor:
+    """``dW[m][k] = sum_b sum_t A_b(m, t) B_b(k, t)`` for batched operands whose contraction index is time.
+
+    ``x_mn == 0``: operand stored (rows, l) per batch entry, ``x_mn == 1``: stored (l, rows).  The output has few
+    tiles and a very long contraction, so the time axis is cut into slices that run as independent batch entries
+    of the split GEMM (one partial product each, through the strided entry point: the slices are views), and the
+    partial products are added afterwards."""
+    tiles = ((m + 127) // 128) * ((k + 255) // 256)
+    slices = 1
+    while tiles * slices * 2 <= 296 and l % (2 * slices) == 0 and (l // (2 * slices)) % 8 == 0 and l // (2 * slices) >= 512:
+        slices *= 2
+    ls = l // slices
+    lib = _lib.load()
+    part = torch.empty(b, slices, m, k, device=A.device, dtype=torch.float32)
+    a_rows, b_rows = (m, k)
+    lda, ldb = (l if a_mn == 0 else a_rows), (l if b_mn == 0 else b_rows)
+    a_step = ls if a_mn == 0 else ls * a_rows           # floats between consecutive time slices
+    b_step = ls if b_mn == 0 else ls * b_rows
+    with torch.cuda.device(A.device):
+        ws = _workspace(lib.aussm_b200_gemm_split3_workspace_bytes(m, k, ls, slices, a_mn, 1, b_mn, 1), A.device)
+        for i in range(b):
+            rc = lib.aussm_b200_gemm_split3_strided(
+                A[i].data_ptr(), a_mn, lda, a_step, B[i].data_ptr(), b_mn, ldb, b_step, part[i].data_ptr(), k, m * k, m, k,
+                ls, slices, 0, 0, _ptr(ws), ws.numel(), _stream(A))
+            _lib.check(rc, "weight gradient (split GEMM)")
+    return part.sum((0, 1))
+
+
 class _ProjectTokens(torch.autograd.Function):
     """out[b] (m, l) = W (m, k) x[b]^T  for token-major x (b, l, k)."""
 
@@ -140,9 +168,8 @@ class _ProjectTokens(torch.autograd.Function):
         g = g.contiguous()
         dW = dx = None
         if ctx.needs_input_grad[0]:
-            dW = torch.empty_like(W)
             # dW (m, k) = sum_b g[b] (m, K = l: K-major) x[b] (K = l rows, k contiguous: MN-major)
-            _gemm(g, 0, 1, x, 1, 1, dW, m, k, l, b, 1)
+            dW = _weight_grad(g, 0, x, 1, m, k, l, b)
         if ctx.needs_input_grad[1]:
             dx = torch.empty_like(x)
             # dx[b] (l, k) = g[b]^T (l, K = m) W (K = m, k): g[b] stored (K rows, l contiguous) and W stored
@@ -192,10 +219,9 @@ class _ProjectBack(torch.autograd.Function):
         g = g.contiguous()
         dW = dy = None
         if ctx.needs_input_grad[0]:
-            dW = torch.empty_like(W)
             # dW (m, k) = sum_b g[b]^T (m, K = l) y[b]^T (K = l, k): g[b] stored (K = l rows, m contiguous)
             # MN-major, y[b] stored (k rows, K = l contiguous) K-major
-            _gemm(g, 1, 1, y, 0, 1, dW, m, k, l, b, 1)
+            dW = _weight_grad(g, 1, y, 0, m, k, l, b)
         if ctx.needs_input_grad[1]:
             dy = torch.empty_like(y)
             # dy[b] (k, l) = W^T (k, K = m) g[b]^T (K = m, l): W stored (K rows, k contiguous) MN-major, shared;

@@ -57,10 +57,10 @@ class _Projection(torch.autograd.Function):
         m, d = W.shape
         b, _, l = u.shape
         g = g.contiguous()
-        dW = torch.empty_like(W)
         du = torch.empty_like(u)
         # dW (m, d) = sum_b g[b] (m, K = l) . u[b] (d, K = l)^T : both K-major, reduced over the batch
-        _gemm(g, 0, 1, u, 0, 1, dW, m, d, l, b, 1)
+        from .stages import _weight_grad
+        dW = _weight_grad(g, 0, u, 0, m, d, l, b)
         # du[b] (d, l) = W^T g[b]: W stored (K = m, rows d) -> MN-major shared; g[b] stored (K = m, cols l) -> MN-major
         _gemm(W, 1, 0, g, 1, 1, du, d, l, m, b, 0)
         return dW, du

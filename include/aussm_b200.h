@@ -58,14 +58,16 @@ unsigned long long aussm_b200_kernel_launches(void);
 
 /* Process-wide option (one atomic word, read at the start of every operator
  * call on whatever thread makes it - framework autograd engines run backward
- * calls on threads of their own).  The only name is "window_steps": steps per
+ * calls on threads of their own).  "window_steps": steps per
  * time window of the windowed operators (rounded up to a multiple of 64; 0 =
  * automatic, about 2 GiB of phases per window).  It decides the layout of the
  * workspace and of a kept-phase buffer, so it is meant to be set once, before
  * the calls that should see it: a kept-phase backward call refuses a buffer
  * that was written under another value, and a call given a workspace sized
  * under another value returns AUSSM_EWORKSPACE; neither computes with a wrong
- * layout.  Returns AUSSM_EINVAL for an unknown name. */
+ * layout.  "time_split" (default 1): 0 turns the time-axis split of under-filled
+ * scans off (see aussm_b200_scan_unitary_fwd_ws); it changes workspace sizes
+ * too.  Returns AUSSM_EINVAL for an unknown name. */
 int aussm_b200_set_option(const char* name, int value);
 
 /* ---- scan core: the phase tensor theta is an input ----------------------
@@ -78,6 +80,27 @@ int aussm_b200_scan_unitary_fwd(const float* theta, const float* u, const float*
                                 const float* Dskip, const float* h0_re, const float* h0_im, /* may be NULL (= 0) */
                                 float* y, float* h1_re, float* h1_im, /* h1 may be NULL */
                                 int B, int D, int N, int L, aussm_stream_t stream);
+
+/* Time-axis split.  The scans walk time sequentially and get their parallelism
+ * from the B*D channels (the reference gets it from block scans over time,
+ * ssm_adaptive_unitary_forward.cu:122-144, reverse_scan.h:152-302).  When the
+ * channels fill less than a quarter of the GPU, the launch is cut into equal
+ * time segments per channel: an aggregate pass gives every segment's end state
+ * from zero and the product of its rotations, a short chain over the segments
+ * gives every segment its true initial state (backward: its end state and the
+ * incoming gradient, the rotations being invertible), and the real pass then
+ * runs all segments side by side.  Same results up to float32 rounding.  The
+ * split needs scratch: aussm_b200_scan_unitary_fwd_ws is
+ * aussm_b200_scan_unitary_fwd with a workspace of
+ * aussm_b200_scan_unitary_fwd_workspace_bytes bytes (0 = this shape is not
+ * split and the workspace may be NULL); the backward entry point and the drop-in
+ * operators split by themselves inside the workspaces they already take. */
+size_t aussm_b200_scan_unitary_fwd_workspace_bytes(int B, int D, int N, int L);
+int aussm_b200_scan_unitary_fwd_ws(const float* theta, const float* u, const float* dt, const float* z,
+                                   const float* B_r, const float* B_theta, const float* C_r, const float* C_theta,
+                                   const float* Dskip, const float* h0_re, const float* h0_im, float* y, float* h1_re,
+                                   float* h1_im, int B, int D, int N, int L, void* workspace, size_t workspace_bytes,
+                                   aussm_stream_t stream);
 
 /* Scratch (bytes) the backward scan needs behind `workspace`. */
 size_t aussm_b200_scan_unitary_bwd_workspace_bytes(int B, int D, int N, int L);
@@ -150,6 +173,14 @@ size_t aussm_b200_gemm_split3_workspace_bytes(int M, int N, int K, int batches, 
 int aussm_b200_gemm_split3(const float* A, int a_mn_major, int a_batched, const float* Bm, int b_mn_major,
                            int b_batched, float* C, int M, int N, int K, int batches, int reduce_batches, int beta,
                            void* workspace, size_t workspace_bytes, aussm_stream_t stream);
+/* The same product on operands that are views of larger arrays: lda / ldb / ldc are the pitches of the slower
+ * index in floats, x_batch_stride the distance between batch entries in floats (0 = the operand is shared by
+ * all batch entries).  Same workspace size as the packed form. */
+int aussm_b200_gemm_split3_strided(const float* A, int a_mn_major, long long lda, long long a_batch_stride,
+                                   const float* Bm, int b_mn_major, long long ldb, long long b_batch_stride, float* C,
+                                   long long ldc, long long c_batch_stride, int M, int N, int K, int batches,
+                                   int reduce_batches, int beta, void* workspace, size_t workspace_bytes,
+                                   aussm_stream_t stream);
 
 /* ---- drop-in operators ---------------------------------------------------
  * aussm_b200_unitary_fwd replaces ssm_adaptive_cuda_forward_unitary

@@ -236,3 +236,60 @@ def test_full_size_properties():
     for k in small:
         assert torch.allclose(small[k], 2 * ref_small[k], rtol=1e-5, atol=0), k     # summed in float32 after a polar map
     assert aussm_b200.device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(1, 6, 16, 4096), (2, 3, 4, 2048), (1, 2, 32, 8192), (1, 40, 16, 1024)])
+def test_time_axis_split_agrees_with_the_sequential_scan(shape):
+    """Few channels: the launch is cut into time segments (aggregate pass, chain over the segments, real pass).
+    Forward and backward must agree with the unsplit kernels to float32 rounding, and with the float64 oracle."""
+    b, d, n, l = shape
+    lib = _lib.load()
+    assert lib.aussm_b200_scan_unitary_fwd_workspace_bytes(b, d, n, l) > 0, "this shape should be split"
+    inp = scan_core_inputs(300 + sum(shape), *shape)
+
+    def run():
+        a, y, hr, hi = _gpu(inp)
+        ((y * inp["gy"].cuda()).sum() + (hr * inp["gh_re"].cuda()).sum() + (hi * inp["gh_im"].cuda()).sum()).backward()
+        return [y.detach(), hr.detach(), hi.detach()] + [t.grad for t in a]
+
+    split = run()
+    try:
+        _lib.set_option("time_split", 0)
+        assert lib.aussm_b200_scan_unitary_fwd_workspace_bytes(b, d, n, l) == 0
+        plain = run()
+    finally:
+        _lib.set_option("time_split", 1)
+    names = ["y", "h_re", "h_im"] + ["grad_" + k for k in KEYS]
+    for name, p, q in zip(names, split, plain):
+        assert scaled_error(p, q) < 2e-5, name
+    a64, y64, hr64, hi64 = _oracle(inp, torch.float64)
+    ((y64 * inp["gy"].double()).sum() + (hr64 * inp["gh_re"].double()).sum() + (hi64 * inp["gh_im"].double()).sum()).backward()
+    assert_parity("y (split)", split[0], y64, scaled_tol=2e-5)
+    for k, g, t in zip(KEYS, split[3:], a64):
+        assert_parity("grad_" + k + " (split)", g, t.grad, atol=1e-5 * float(t.grad.abs().max()) + 1e-9, rtol=1e-3,
+                      scaled_tol=1e-4)
+    assert aussm_b200.device_status() == 0
+
+
+def test_time_axis_split_in_the_drop_in_operator():
+    """The windowed operator splits its scans too (few channels, long windows); same result as without."""
+    from tests.helpers import NAMES, model_like_inputs
+    inp = model_like_inputs(55, 1, 8, 16, 2048)
+
+    def run():
+        args = [inp[k].cuda().clone().requires_grad_(True) for k in NAMES]
+        y = aussm_b200.ssm_adaptive_interface(*args, unitary=True)
+        (y * inp["gy"].cuda()).sum().backward()
+        return [y.detach()] + [a.grad for a in args]
+
+    split = run()
+    try:
+        _lib.set_option("time_split", 0)
+        plain = run()
+    finally:
+        _lib.set_option("time_split", 1)
+    for name, p, q in zip(["y"] + NAMES, split, plain):
+        if p.is_complex():
+            p, q = torch.view_as_real(p), torch.view_as_real(q)
+        assert scaled_error(p, q) < 5e-5, name
+    assert aussm_b200.device_status() == 0
