@@ -294,16 +294,19 @@ class ScanCore:
         self.small = [torch.empty(n, device=dev) for _ in range(4)] + [torch.empty(d, device=dev)]
         self.ws = torch.empty(lib.aussm_b200_scan_unitary_bwd_workspace_bytes(b, d, n, l), dtype=torch.uint8,
                               device=dev)
+        # non-empty only when the launch is cut into time segments (few channels)
+        self.fws = torch.empty(max(16, lib.aussm_b200_scan_unitary_fwd_workspace_bytes(b, d, n, l)), dtype=torch.uint8,
+                               device=dev)
         self.stream = torch.cuda.current_stream().cuda_stream
 
     def fwd(self):
         from aussm_b200 import _lib
         i, P = self.inp, (lambda t: t.data_ptr())
         b, d, n, l = self.shape
-        rc = self.lib.aussm_b200_scan_unitary_fwd(P(i["theta"]), P(i["u"]), P(i["dt"]), P(i["z"]), P(i["B_r"]),
-                                                  P(i["B_theta"]), P(i["C_r"]), P(i["C_theta"]), P(i["D"]), None,
-                                                  None, P(self.y), P(self.h_re), P(self.h_im), b, d, n, l,
-                                                  self.stream)
+        rc = self.lib.aussm_b200_scan_unitary_fwd_ws(P(i["theta"]), P(i["u"]), P(i["dt"]), P(i["z"]), P(i["B_r"]),
+                                                     P(i["B_theta"]), P(i["C_r"]), P(i["C_theta"]), P(i["D"]), None,
+                                                     None, P(self.y), P(self.h_re), P(self.h_im), b, d, n, l,
+                                                     P(self.fws), self.fws.numel(), self.stream)
         _lib.check(rc, "scan forward")
 
     def bwd(self):
@@ -452,10 +455,21 @@ def run_only(args):
     b, d, n, l = args.batch, args.d_inner, args.d_state, args.seq_len
     if args.only == "scan":
         from aussm_b200 import _lib
-        core = ScanCore(_lib.load(), b, d, n, l, torch.device("cuda", 0), 1234)
-        ms, f, bw, _ = core.time(args.steps, args.warmup, torch.cuda.synchronize)
-        out = {"kind": "unitary scan core", "batch": b, "d_inner": d, "d_state": n, "seq_len": l, "ms_fwd": f,
-               "ms_bwd": bw, "ms_fwd_bwd": ms}
+        lib = _lib.load()
+        out = {"kind": "unitary scan core", "batch": b, "d_inner": d, "d_state": n, "seq_len": l}
+        # with and without the time-axis split (it only engages when the channels under-fill the GPU)
+        for tag, on in (("", 1), ("_no_time_split", 0)):
+            _lib.set_option("time_split", on)
+            split = lib.aussm_b200_scan_unitary_fwd_workspace_bytes(b, d, n, l) > 0
+            if not on and "time_split" in out and not out["time_split"]:
+                break
+            core = ScanCore(lib, b, d, n, l, torch.device("cuda", 0), 1234)
+            ms, f, bw, _ = core.time(args.steps, args.warmup, torch.cuda.synchronize)
+            out.update({"ms_fwd" + tag: f, "ms_bwd" + tag: bw, "ms_fwd_bwd" + tag: ms})
+            if on:
+                out["time_split"] = split
+            del core
+        _lib.set_option("time_split", 1)
     elif args.only == "gemm":
         out = gemm_case(*args.gemm_shape, args.steps, args.warmup)
     elif args.only == "dropin":

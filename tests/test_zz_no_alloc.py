@@ -50,8 +50,14 @@ def _run_both(seed, b, d, n, l):
                 P(o["dC_r"]), P(o["dC_t"]), P(o["dD"]), P(o["dh_re"]), P(o["dh_im"]), b, d, n, l]
 
     ref = outputs()
-    ws = torch.empty(lib.aussm_b200_scan_unitary_bwd_workspace_bytes(b, d, n, l), dtype=torch.uint8, device="cuda")
-    _lib.check(lib.aussm_b200_scan_unitary_bwd(*common(ref), P(ws), ws.numel(), stream), "regular backward")
+    # The regular entry point may cut a launch with few channels into time segments (other kernels, other
+    # rounding); the static one never does.  Compare like with like: the split is off for the reference call.
+    _lib.set_option("time_split", 0)
+    try:
+        ws = torch.empty(lib.aussm_b200_scan_unitary_bwd_workspace_bytes(b, d, n, l), dtype=torch.uint8, device="cuda")
+        _lib.check(lib.aussm_b200_scan_unitary_bwd(*common(ref), P(ws), ws.numel(), stream), "regular backward")
+    finally:
+        _lib.set_option("time_split", 1)
     got = outputs()
     _lib.check(lib.aussm_b200_scan_unitary_bwd_static(*common(got), stream), "static backward")
     torch.cuda.synchronize()
