@@ -1,11 +1,14 @@
 // General complex / positive-real diagonal selective scan for sm_100a.
 //
 // Same decomposition as scan_unitary.cu and scan_s6.cu: one thread per state
-// and channel, sequential in time; one independent warp per 32/NL channels of
-// one batch entry; 16-step tiles staged by coalesced 16-byte asynchronous
-// copies in a two-stage ring.  A thread consumes its own rho and theta rows
-// (like the unitary scan) and the B_j, C_j rows of its batch entry (like the
-// S6 scan).  |lambda| != 1, so the recurrence is not reversible: the forward
+// and channel, sequential in time; one warp per 32/NL channels of one batch
+// entry; 16-step tiles staged by coalesced 16-byte asynchronous copies in a
+// two-stage ring.  A thread consumes its own rho and theta rows (like the
+// unitary scan) and the B_j, C_j rows of its batch entry (like the S6 scan).
+// The B / C rows are the same for every channel of a batch entry, so the warps
+// of a block (all of one batch entry) share one copy of them: each warp fetches
+// its share, two block barriers per tile make the copy visible and protect it
+// from being refilled early.  |lambda| != 1, so the recurrence is not reversible: the forward
 // kernel records the state at every tile start, the backward kernel recomputes
 // a tile's states from there and walks it in reverse.
 //
@@ -13,10 +16,9 @@
 // two streams in flight), so the tiles are short (16 steps) and every cell is
 // used several times: the backward kernel's recomputing pass overwrites the
 // rho / theta cells it has consumed with lambda (the reverse pass then needs no
-// second exponential and sine / cosine), and parks the state before each step
-// in the two column-sum tiles; the reverse pass replaces lambda by drho /
-// dtheta, which leave with coalesced stores, and the parked states by the
-// per-state terms of the column sums.  dB and dC (sums over the channels of a
+// second exponential and sine / cosine) and keeps the state before each step in
+// registers; the reverse pass replaces lambda by drho / dtheta, which leave
+// with coalesced stores.  dB and dC (sums over the channels of a
 // batch entry) use shuffles and vector float atomics, as the reference's
 // kernels do (ssm_adaptive_complex.cu:358-660).
 #include "scan_complex.cuh"
@@ -41,19 +43,22 @@ template <int NL_, bool BWD_>
 struct CCfg {
     static constexpr int NL = NL_;
     static constexpr int CPW = 32 / NL;
+    // warps per block: they share the B / C tiles of their batch entry (one-warp blocks for few states per
+    // channel, where those tiles are small anyway)
+    static constexpr int WARPS = NL >= 8 ? (BWD_ ? 6 : 4) : 1;
     static constexpr int AUX = BWD_ ? 4 : 3;                      // u, dt, z [, gy]
     static constexpr int OWN_ROWS = 64;                           // rho rows then theta rows, one per lane
     static constexpr int BC_ROWS = 4 * NL;                        // B_re, B_im, C_re, C_im
-    static constexpr int STAGE_FLOATS = (OWN_ROWS + BC_ROWS) * TP + CPW * AUX * T;
-    // not staged.  forward: s row + p tile.  backward: s, w, d silu(u)/du rows + two tiles (state before each
-    // step, then the per-state terms of the two column sums)
+    static constexpr int STAGE_FLOATS = OWN_ROWS * TP + CPW * AUX * T;      // per warp
+    static constexpr int BC_FLOATS = BC_ROWS * TP;                          // per block
+    // not staged.  forward: s row + p tile.  backward: s, w, d silu(u)/du rows + the tiles of the two column sums
     static constexpr int ROWS = BWD_ ? 3 : 1;
     static constexpr int TILES = BWD_ ? 2 : 1;
     static constexpr int SCRATCH_FLOATS = CPW * ROWS * T + TILES * 32 * TP;
     static constexpr int WARP_FLOATS = STAGES * STAGE_FLOATS + SCRATCH_FLOATS;
-    static constexpr size_t SMEM_BYTES = (size_t)WARP_FLOATS * sizeof(float);
+    static constexpr size_t SMEM_BYTES = (size_t)(STAGES * BC_FLOATS + WARPS * WARP_FLOATS) * sizeof(float);
     static constexpr int NCH_OWN = OWN_ROWS * NQ / 32;
-    static constexpr int NCH_BC = (BC_ROWS * NQ + 31) / 32;
+    static constexpr int NCH_BC = (BC_ROWS * NQ + 32 * WARPS - 1) / (32 * WARPS);   // this warp's share
     static constexpr int NCH_AUX = (CPW * AUX * NQ + 31) / 32;
     // per-(channel, step) passes: CPW * T elements over 32 lanes
     static constexpr int ELEMS = CPW * T;
@@ -68,8 +73,8 @@ struct CMap {
     const float* bc_ptr[C::NCH_BC];
     const float* aux_ptr[C::NCH_AUX];
 
-    __device__ __forceinline__ void init(int lane, int nvalid, int N, const float* rho_b, const float* theta_b,
-                                         long long ld_lam, int i0, const float* const* bc_src,
+    __device__ __forceinline__ void init(int lane, int warp, int nvalid, int N, const float* rho_b,
+                                         const float* theta_b, long long ld_lam, int i0, const float* const* bc_src,
                                          const float* const* aux_src, long long ch0, long long ld_row) {
 #pragma unroll
         for (int i = 0; i < C::NCH_OWN; ++i) {
@@ -83,7 +88,7 @@ struct CMap {
         }
 #pragma unroll
         for (int i = 0; i < C::NCH_BC; ++i) {
-            const int id = i * 32 + lane;
+            const int id = (i * C::WARPS + warp) * 32 + lane;      // piece of the block's B / C tile
             const int row = id / NQ, col = id % NQ;
             bc_ptr[i] = nullptr;
             if (row < C::BC_ROWS) {
@@ -104,9 +109,9 @@ struct CMap {
         }
     }
 
-    __device__ __forceinline__ void issue(float* stage, long long t0, int tlen, int lane) const {
-        float* bc = stage + C::OWN_ROWS * TP;
-        float* aux = bc + C::BC_ROWS * TP;
+    // stage: this warp's rows; bc: the block's B / C tile of the same stage
+    __device__ __forceinline__ void issue(float* stage, float* bc, long long t0, int tlen, int lane, int warp) const {
+        float* aux = stage + C::OWN_ROWS * TP;
         const int col = lane % NQ, r0 = lane / NQ;                 // piece i of this lane: row i * (32 / NQ) + r0
         constexpr int RPI = 32 / NQ;
         if (col * 4 < tlen) {
@@ -115,7 +120,8 @@ struct CMap {
                 if (own_ptr[i] != nullptr) cp_async16(stage + (i * RPI + r0) * TP + col * 4, own_ptr[i] + t0);
 #pragma unroll
             for (int i = 0; i < C::NCH_BC; ++i)
-                if (bc_ptr[i] != nullptr) cp_async16(bc + (i * RPI + r0) * TP + col * 4, bc_ptr[i] + t0);
+                if (bc_ptr[i] != nullptr)
+                    cp_async16(bc + ((i * C::WARPS + warp) * RPI + r0) * TP + col * 4, bc_ptr[i] + t0);
 #pragma unroll
             for (int i = 0; i < C::NCH_AUX; ++i)
                 if (aux_ptr[i] != nullptr) cp_async16(aux + (i * RPI + r0) * T + col * 4, aux_ptr[i] + t0);
@@ -126,12 +132,18 @@ struct CMap {
 
 // rows that are never copied (null inputs) must read as zero
 template <class C>
-__device__ __forceinline__ void zero_stages(float* smem, int lane) {
+__device__ __forceinline__ void zero_stages(float* bc_ring, float* wsm, int lane) {
+    for (int i = threadIdx.x; i < STAGES * C::BC_FLOATS; i += C::WARPS * 32) bc_ring[i] = 0.f;
     for (int s = 0; s < STAGES; ++s) {
-        float* st = smem + s * C::STAGE_FLOATS;
-        for (int i = lane; i < (C::OWN_ROWS + C::BC_ROWS) * TP; i += 32) st[i] = 0.f;
+        float* st = wsm + s * C::STAGE_FLOATS;
+        for (int i = lane; i < C::OWN_ROWS * TP; i += 32) st[i] = 0.f;
     }
-    __syncwarp();
+    if (C::WARPS > 1) __syncthreads(); else __syncwarp();
+}
+
+template <class C>
+__device__ __forceinline__ void block_sync() {
+    if (C::WARPS > 1) __syncthreads(); else __syncwarp();
 }
 
 // lambda = exp(rho + i theta) for four steps
@@ -154,16 +166,23 @@ __device__ __forceinline__ void lambda4(const float4 r4, const float4 t4, float 
 // Forward
 // ---------------------------------------------------------------------------
 template <int NL>
-__global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
+__global__ void __launch_bounds__(CCfg<NL, false>::WARPS * 32) cplx_fwd_kernel(const CplxFwdParams p) {
     using C = CCfg<NL, false>;
     constexpr int CPW = C::CPW, AUX = C::AUX, VW = C::VW;
-    extern __shared__ __align__(128) float smem[];
-    const int lane = threadIdx.x;
+    extern __shared__ __align__(128) float smem_all[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // a block = WARPS consecutive tasks (32/NL channels each) of one batch entry; a warp beyond the last task
+    // shadows it (it takes part in the copies of the shared tile and in the barriers, and stores nothing)
     const int tasks_per_batch = (p.Dmod + CPW - 1) / CPW;
-    const int b = blockIdx.x / tasks_per_batch, tw = blockIdx.x % tasks_per_batch;
+    const int blocks_per_batch = (tasks_per_batch + C::WARPS - 1) / C::WARPS;
+    const int b = blockIdx.x / blocks_per_batch;
+    const int tw_raw = (blockIdx.x % blocks_per_batch) * C::WARPS + warp;
+    const int tw = min(tw_raw, tasks_per_batch - 1);
     const int i0 = tw * CPW;
-    const int nvalid = min(CPW, p.Dmod - i0);
+    const int nvalid = tw_raw < tasks_per_batch ? min(CPW, p.Dmod - i0) : 0;
     const long long ch0 = (long long)b * p.Dmod + i0;
+    float* bc_ring = smem_all;
+    float* smem = smem_all + STAGES * C::BC_FLOATS + warp * C::WARP_FLOATS;
     const int c = lane / NL, j = lane % NL;
     const bool act = c < nvalid && j < p.N;
     const int N = p.N, L = p.L;
@@ -172,7 +191,7 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
 
     float* srow = smem + STAGES * C::STAGE_FLOATS;          // [CPW][T]: s = dt silu(u)
     float* pt = srow + CPW * C::ROWS * T;                   // [32][TP]
-    zero_stages<C>(smem, lane);
+    zero_stages<C>(bc_ring, smem, lane);
 
     float2* rec = (p.states && act) ? reinterpret_cast<float2*>(p.states) + (ch * N + j) * p.states_stride + p.tile0
                                     : nullptr;
@@ -193,21 +212,23 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
     const float* aux_src[AUX] = {p.u, p.dt, p.z};
     const long long lam_b = (long long)b * p.lam_batch_stride;
     CMap<C> map;
-    map.init(lane, nvalid, N, p.rho ? p.rho + lam_b : nullptr, p.theta ? p.theta + lam_b : nullptr, p.ld_lam, i0,
-             bc_src, aux_src, ch0, p.ld_row);
+    map.init(lane, warp, nvalid, N, p.rho ? p.rho + lam_b : nullptr, p.theta ? p.theta + lam_b : nullptr, p.ld_lam,
+             i0, bc_src, aux_src, ch0, p.ld_row);
     for (int s = 0; s < STAGES; ++s) {
-        if (s < ntiles) map.issue(smem + s * C::STAGE_FLOATS, (long long)s * T, min(T, L - s * T), lane);
+        if (s < ntiles)
+            map.issue(smem + s * C::STAGE_FLOATS, bc_ring + s * C::BC_FLOATS, (long long)s * T, min(T, L - s * T), lane,
+                      warp);
         else cp_async_commit();
     }
 
     for (int tile = 0; tile < ntiles; ++tile) {
         float* st = smem + (tile % STAGES) * C::STAGE_FLOATS;
-        float* bc = st + C::OWN_ROWS * TP;
-        float* aux = bc + C::BC_ROWS * TP;
+        float* bc = bc_ring + (tile % STAGES) * C::BC_FLOATS;
+        float* aux = st + C::OWN_ROWS * TP;
         const long long t0 = (long long)tile * T;
         const int tlen = min(T, L - (int)t0);
         cp_async_wait<STAGES - 1>();
-        __syncwarp();
+        block_sync<C>();                                    // every warp's share of the B / C tile has landed
         if (rec) rec[tile] = make_float2(hr, hi);
         // pre-pass: silu(u) replaces u, s = dt silu(u)
 #pragma unroll
@@ -279,9 +300,9 @@ __global__ void __launch_bounds__(32) cplx_fwd_kernel(const CplxFwdParams p) {
                 acc.st(p.y + (ch0 + cc) * p.ld_row + t0 + t);
             }
         }
-        __syncwarp();
+        block_sync<C>();                                    // nobody reads this stage's B / C tile any more
         const int nt = tile + STAGES;
-        if (nt < ntiles) map.issue(st, (long long)nt * T, min(T, L - nt * T), lane);
+        if (nt < ntiles) map.issue(st, bc, (long long)nt * T, min(T, L - nt * T), lane, warp);
         else cp_async_commit();
     }
     cp_async_wait<0>();
@@ -298,16 +319,22 @@ __device__ __forceinline__ void red_add_v4c(float* addr, const float (&v)[4]) {
 }
 
 template <int NL>
-__global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
+__global__ void __launch_bounds__(CCfg<NL, true>::WARPS * 32, CCfg<NL, true>::WARPS > 1 ? 2 : 1)
+cplx_bwd_kernel(const CplxBwdParams p) {
     using C = CCfg<NL, true>;
     constexpr int CPW = C::CPW, AUX = C::AUX, VW = C::VW;
-    extern __shared__ __align__(128) float smem[];
-    const int lane = threadIdx.x;
+    extern __shared__ __align__(128) float smem_all[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int tasks_per_batch = (p.Dmod + CPW - 1) / CPW;
-    const int b = blockIdx.x / tasks_per_batch, tw = blockIdx.x % tasks_per_batch;
+    const int blocks_per_batch = (tasks_per_batch + C::WARPS - 1) / C::WARPS;
+    const int b = blockIdx.x / blocks_per_batch;
+    const int tw_raw = (blockIdx.x % blocks_per_batch) * C::WARPS + warp;
+    const int tw = min(tw_raw, tasks_per_batch - 1);          // warps beyond the last task shadow it
     const int i0 = tw * CPW;
-    const int nvalid = min(CPW, p.Dmod - i0);
+    const int nvalid = tw_raw < tasks_per_batch ? min(CPW, p.Dmod - i0) : 0;
     const long long ch0 = (long long)b * p.Dmod + i0;
+    float* bc_ring = smem_all;
+    float* smem = smem_all + STAGES * C::BC_FLOATS + warp * C::WARP_FLOATS;
     const int c = lane / NL, j = lane % NL;
     const bool act = c < nvalid && j < p.N;
     const int N = p.N, L = p.L;
@@ -316,9 +343,9 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
     const bool has_rho = p.rho != nullptr, has_theta = p.theta != nullptr;
 
     float* rows = smem + STAGES * C::STAGE_FLOATS;          // [CPW][3][T]: s, w, d silu(u)/du
-    float* et = rows + CPW * C::ROWS * T;                   // [32][TP] Re h_{t-1}, then Re(conj(eta) B)
-    float* pt = et + 32 * TP;                               // [32][TP] Im h_{t-1}, then Re(C h)
-    zero_stages<C>(smem, lane);
+    float* et = rows + CPW * C::ROWS * T;                   // [32][TP] Re(conj(eta) B)
+    float* pt = et + 32 * TP;                               // [32][TP] Re(C h)
+    zero_stages<C>(bc_ring, smem, lane);
 
     const long long rec_off = (ch * N + j) * p.states_stride + p.tile0;
     const float2* rec = reinterpret_cast<const float2*>(p.states) + (act ? rec_off : 0);
@@ -347,11 +374,13 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
     const float* aux_src[AUX] = {p.u, p.dt, p.z, p.gy};
     const long long lam_b = (long long)b * p.lam_batch_stride;
     CMap<C> map;
-    map.init(lane, nvalid, N, has_rho ? p.rho + lam_b : nullptr, has_theta ? p.theta + lam_b : nullptr, p.ld_lam, i0,
-             bc_src, aux_src, ch0, p.ld_row);
+    map.init(lane, warp, nvalid, N, has_rho ? p.rho + lam_b : nullptr, has_theta ? p.theta + lam_b : nullptr,
+             p.ld_lam, i0, bc_src, aux_src, ch0, p.ld_row);
     for (int r = 0; r < STAGES; ++r) {
         const int tile = ntiles - 1 - r;
-        if (tile >= 0) map.issue(smem + r * C::STAGE_FLOATS, (long long)tile * T, min(T, L - tile * T), lane);
+        if (tile >= 0)
+            map.issue(smem + r * C::STAGE_FLOATS, bc_ring + r * C::BC_FLOATS, (long long)tile * T,
+                      min(T, L - tile * T), lane, warp);
         else cp_async_commit();
     }
     float2 h_next = act ? rec[ntiles - 1] : make_float2(0.f, 0.f);
@@ -359,15 +388,15 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
     for (int r = 0; r < ntiles; ++r) {
         const int tile = ntiles - 1 - r;
         float* st = smem + (r % STAGES) * C::STAGE_FLOATS;
-        float* bc = st + C::OWN_ROWS * TP;
-        float* aux = bc + C::BC_ROWS * TP;
+        float* bc = bc_ring + (r % STAGES) * C::BC_FLOATS;
+        float* aux = st + C::OWN_ROWS * TP;
         const long long t0 = (long long)tile * T;
         const int tlen = min(T, L - (int)t0);
         const int nq = tlen >> 2;
         float hr = h_next.x, hi = h_next.y;                 // state before the tile's first step
         if (tile > 0 && act) h_next = rec[tile - 1];
         cp_async_wait<STAGES - 1>();
-        __syncwarp();
+        block_sync<C>();                                    // every warp's share of the B / C tile has landed
 
         // pre-pass: every activation once.  s = dt silu(u) and w = gy silu(z) feed the scan; silu(u) and
         // d silu(z)/dz replace the u and z cells, d silu(u)/du gets a row of its own.
@@ -398,7 +427,9 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
         }
         __syncwarp();
 
-        // recompute the tile's states: lambda replaces (rho, theta), the state before each step is parked
+        // recompute the tile's states: lambda replaces (rho, theta) in the stage, the state before each step
+        // stays in registers (the quads of a tile are unrolled, so the arrays are indexed statically)
+        float hpr[T], hpi[T];
         auto recompute = [&](const int q) {
             const float4 s4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
@@ -407,11 +438,10 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
             lambda4(ld_shared_f4(st + lane * TP + 4 * q), ld_shared_f4(st + (32 + lane) * TP + 4 * q), lr, li);
             const float sv[4] = AUSSM_F4(s4);
             const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
-            float pr[4], pi[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                pr[e] = hr;
-                pi[e] = hi;
+                hpr[4 * q + e] = hr;
+                hpi[4 * q + e] = hi;
                 const float nr = fmaf(lr[e], hr, fmaf(-li[e], hi, sv[e] * brv[e]));
                 const float ni = fmaf(lr[e], hi, fmaf(li[e], hr, sv[e] * biv[e]));
                 hr = nr;
@@ -419,8 +449,6 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
             }
             st_shared_f4(st + lane * TP + 4 * q, make_float4(lr[0], lr[1], lr[2], lr[3]));
             st_shared_f4(st + (32 + lane) * TP + 4 * q, make_float4(li[0], li[1], li[2], li[3]));
-            st_shared_f4(et + lane * TP + 4 * q, make_float4(pr[0], pr[1], pr[2], pr[3]));
-            st_shared_f4(pt + lane * TP + 4 * q, make_float4(pi[0], pi[1], pi[2], pi[3]));
         };
         // reverse pass
         auto reverse = [&](const int q) {
@@ -432,13 +460,12 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
             const float4 ci4 = ld_shared_f4(bc + (3 * NL + j) * TP + 4 * q);
             const float4 lr4 = ld_shared_f4(st + lane * TP + 4 * q);
             const float4 li4 = ld_shared_f4(st + (32 + lane) * TP + 4 * q);
-            const float4 pr4 = ld_shared_f4(et + lane * TP + 4 * q);
-            const float4 pi4 = ld_shared_f4(pt + lane * TP + 4 * q);
             const float sv[4] = AUSSM_F4(s4), wv[4] = AUSSM_F4(w4);
             const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
             const float crv[4] = AUSSM_F4(cr4), civ[4] = AUSSM_F4(ci4);
             const float lr[4] = AUSSM_F4(lr4), li[4] = AUSSM_F4(li4);
-            const float prv[4] = AUSSM_F4(pr4), piv[4] = AUSSM_F4(pi4);
+            const float prv[4] = {hpr[4 * q], hpr[4 * q + 1], hpr[4 * q + 2], hpr[4 * q + 3]};
+            const float piv[4] = {hpi[4 * q], hpi[4 * q + 1], hpi[4 * q + 2], hpi[4 * q + 3]};
             float dr[4], dth[4], E[4], P[4], gBr[4], gBi[4], gCr[4], gCi[4];
 #pragma unroll
             for (int e = 3; e >= 0; --e) {
@@ -482,7 +509,7 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
                     for (int e = 0; e < 4; ++e) gCi[e] += __shfl_xor_sync(0xffffffffu, gCi[e], off);
                 }
             }
-            if (c == 0 && j < N) {
+            if (c == 0 && j < N && nvalid > 0) {
                 const long long o = bo + (long long)j * p.ld_row + t0 + 4 * q;
                 red_add_v4c(p.dB_re + o, gBr);
                 red_add_v4c(p.dC_re + o, gCr);
@@ -490,15 +517,12 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
                 if (p.dC_im) red_add_v4c(p.dC_im + o, gCi);
             }
         };
-        if (tlen == T) {
 #pragma unroll
-            for (int q = 0; q < NQ; ++q) recompute(q);
+        for (int q = 0; q < NQ; ++q)
+            if (q < nq) recompute(q);
 #pragma unroll
-            for (int q = NQ - 1; q >= 0; --q) reverse(q);
-        } else {
-            for (int q = 0; q < nq; ++q) recompute(q);
-            for (int q = nq - 1; q >= 0; --q) reverse(q);
-        }
+        for (int q = NQ - 1; q >= 0; --q)
+            if (q < nq) reverse(q);
         // the gradient of the recorded state at this tile's start joins the carry
         if (grec) {
             const float2 g = grec[tile];
@@ -559,11 +583,11 @@ __global__ void __launch_bounds__(32) cplx_bwd_kernel(const CplxBwdParams p) {
                         ld_shared_f4(st + row * TP + col * 4);
             }
         }
-        __syncwarp();
+        block_sync<C>();                                    // nobody reads this stage's B / C tile any more
         const int nr = r + STAGES;
         if (nr < ntiles) {
             const int nt = ntiles - 1 - nr;
-            map.issue(st, (long long)nt * T, min(T, L - nt * T), lane);
+            map.issue(st, bc, (long long)nt * T, min(T, L - nt * T), lane, warp);
         } else {
             cp_async_commit();
         }
@@ -596,8 +620,9 @@ cudaError_t launch_nl(Kern kern, const Params& p, cudaStream_t stream) {
     using C = CCfg<NL, BWD>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    const long long blocks = (long long)(p.nch / p.Dmod) * ((p.Dmod + C::CPW - 1) / C::CPW);
-    kern<<<(unsigned)blocks, 32, C::SMEM_BYTES, stream>>>(p);
+    const long long tasks = (p.Dmod + C::CPW - 1) / C::CPW;
+    const long long blocks = (long long)(p.nch / p.Dmod) * ((tasks + C::WARPS - 1) / C::WARPS);
+    kern<<<(unsigned)blocks, C::WARPS * 32, C::SMEM_BYTES, stream>>>(p);
     count_launch();
     return cudaGetLastError();
 }
