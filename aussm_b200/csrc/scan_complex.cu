@@ -43,9 +43,11 @@ template <int NL_, bool BWD_>
 struct CCfg {
     static constexpr int NL = NL_;
     static constexpr int CPW = 32 / NL;
-    // warps per block: they share the B / C tiles of their batch entry (one-warp blocks for few states per
-    // channel, where those tiles are small anyway)
-    static constexpr int WARPS = NL >= 8 ? (BWD_ ? 6 : 4) : 1;
+    // warps per block: in the forward kernel they share the B / C tiles of their batch entry (measured 2.55
+    // against 2.75 ms at batch 8 x 2048 channels x 4096 steps).  The backward kernel, and few states per channel
+    // (small tiles anyway), keep one-warp blocks: with six warps sharing the tiles it measured 9.85 against 9.15
+    // ms - its warps drift apart (atomics, long reverse pass) and wait for each other at the two barriers.
+    static constexpr int WARPS = (NL >= 8 && !BWD_) ? 4 : 1;
     static constexpr int AUX = BWD_ ? 4 : 3;                      // u, dt, z [, gy]
     static constexpr int OWN_ROWS = 64;                           // rho rows then theta rows, one per lane
     static constexpr int BC_ROWS = 4 * NL;                        // B_re, B_im, C_re, C_im
@@ -319,7 +321,7 @@ __device__ __forceinline__ void red_add_v4c(float* addr, const float (&v)[4]) {
 }
 
 template <int NL>
-__global__ void __launch_bounds__(CCfg<NL, true>::WARPS * 32, CCfg<NL, true>::WARPS > 1 ? 2 : 1)
+__global__ void __launch_bounds__(CCfg<NL, true>::WARPS * 32)
 cplx_bwd_kernel(const CplxBwdParams p) {
     using C = CCfg<NL, true>;
     constexpr int CPW = C::CPW, AUX = C::AUX, VW = C::VW;

@@ -392,7 +392,7 @@ def variant_case(kind, b, d, n, l, steps, warmup=3, seed=7):
         Bm, Cm = r(b, n, l) * sc, r(b, n, l) * sc
         leaves = [u, dt, z]
         fwd = lambda: selective_scan_fn(u, dt, A, Bm, Cm, D, z=z, delta_softplus=True)
-        bytes_f, bytes_b, bound = 16, 28, "fp32 issue"
+        bytes_f, bytes_b, bound = 16, 28, "shared-memory pipe (0.73 / 0.81 busy: profiles/scan_s6_small.md), not HBM"
     else:
         raise ValueError(kind)
     ms_f = _time_events(lambda: fwd(), steps, warmup)
