@@ -506,11 +506,12 @@ def run_extras(args, dev, world, rank, barrier):
                                    for k in ("real", "complex", "preal", "unitary")]
         torch.cuda.empty_cache()
     train = []
-    for config, micro, steps in ((3, 0, 3), (4, 4, 1)):
+    for config, micro, steps, warm in ((3, 0, 5, 3), (4, 4, 2, 1)):
         model, batch, loss_fn, tokens, local_batch, gb = make_config(config, dev, rank, world)
         opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
         x, y = batch()
-        train_step(model, opt, x, y, loss_fn, world, micro, global_batch=gb)
+        for _ in range(warm):
+            train_step(model, opt, x, y, loss_fn, world, micro, global_batch=gb)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -520,7 +521,7 @@ def run_extras(args, dev, world, rank, barrier):
         barrier()
         ms = max_over_ranks(e0.elapsed_time(e1) / steps, dev, world)
         train.append({"config": config, "ms_per_step": round(ms, 3), "tokens_per_s": round(tokens / ms * 1e3, 1),
-                      "local_batch": local_batch, "micro_batch": micro, "steps": steps,
+                      "local_batch": local_batch, "micro_batch": micro, "steps": steps, "warmup": warm,
                       "allreduce_calls_per_step": ncoll, "loss": loss})
         del model, opt, x, y
         torch.cuda.empty_cache()
