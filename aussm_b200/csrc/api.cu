@@ -395,8 +395,8 @@ size_t aussm_b200_gemm_split3_workspace_bytes(int M, int N, int K, int batches, 
                                               int b_mn_major, int b_batched) {
     if (M <= 0 || N <= 0 || K <= 0 || batches <= 0) return 0;
     const PackedDims a = packed_dims(a_mn_major, M, K), b = packed_dims(b_mn_major, N, K);
-    const size_t na = align_up((size_t)a.rows * a.pitch * (a_batched ? batches : 1), 128);
-    const size_t nb = align_up((size_t)b.rows * b.pitch * (b_batched ? batches : 1), 128);
+    const size_t na = split_part_halves((size_t)a.rows * a.pitch * (a_batched ? batches : 1));
+    const size_t nb = split_part_halves((size_t)b.rows * b.pitch * (b_batched ? batches : 1));
     return 2 * (na + nb) * 2 + 1024;
 }
 
@@ -423,7 +423,8 @@ int aussm_b200_gemm_split3_strided(const float* A, int a_mn_major, long long lda
     }
     cudaStream_t stream = (cudaStream_t)stream_;
     const int na = a_batched ? batches : 1, nb = b_batched ? batches : 1;
-    const size_t a_halves = align_up((size_t)a.rows * a.pitch * na, 128), b_halves = align_up((size_t)b.rows * b.pitch * nb, 128);
+    const size_t a_halves = split_part_halves((size_t)a.rows * a.pitch * na);
+    const size_t b_halves = split_part_halves((size_t)b.rows * b.pitch * nb);
     char* w = static_cast<char*>(workspace);
     void* a_hi = w;
     void* a_lo = w + a_halves * 2;

@@ -10,12 +10,12 @@
 // The power-of-two scales come off exactly in the epilogue.
 //
 // One persistent CTA per SM walks 128 x 256 tiles of C.  Roles: warp 0 = TMA
-// producer (one lane), warp 1 = MMA issuer (one lane; the warp also owns the
-// 512-column TMEM allocation), warps 2-9 = accumulate/epilogue (TMEM ->
-// registers -> global).  Per K block of 64 values and 128-column half of the
-// tile the issuer runs, for each of the four K = 16 slices, one N = 256
-// tcgen05.mma  a_hi x [b_hi | b_lo]  (accumulators [main | cross]) and one
-// N = 128 tcgen05.mma  a_lo x b_hi  (cross).
+// producer, warp 1 = MMA issuer (one lane; the warp also owns the 512-column
+// TMEM allocation), warps 2-5 / 6-9 = accumulate/epilogue of the tile's left /
+// right 128 columns (TMEM -> registers -> shared-memory transpose -> global).
+// Per K block of 64 values and 128-column half of the tile the issuer runs, for
+// each of the four K = 16 slices, one N = 256 tcgen05.mma  a_hi x [b_hi | b_lo]
+// (accumulators [main | cross]) and one N = 128 tcgen05.mma  a_lo x b_hi  (cross).
 //
 // Shared-memory operand tiles use the 128-byte swizzle the TMA engine writes and
 // the MMA descriptors expect.  K-major operand (K contiguous in memory): rows
@@ -43,13 +43,20 @@ namespace aussm {
 namespace {
 
 constexpr int BM = 128, BN = 256;
-constexpr int BK_BYTES = 128;                        // one K block = one 128-byte swizzle row: 64 FP16 values
-constexpr int STAGES = 2;
-constexpr int A_TILE_BYTES = BM * BK_BYTES;          // 16 KB
-constexpr int B_TILE_BYTES = BN * BK_BYTES;          // 32 KB
-constexpr int B_HALF_BYTES = 128 * BK_BYTES;         // one part of one 128-column half: 16 KB
-constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;   // hi + lo of both operands: 96 KB
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + slack for 1024-byte alignment
+constexpr int BK = 64;                               // K values per block
+constexpr int KROW_BYTES = BK * 2;                   // a K-major row of a block: one swizzle row (128 or 64 bytes)
+constexpr int MNBOX = 64;                            // row elements per MN-major TMA box (128-byte swizzle rows)
+constexpr int MNBOX_BYTES = MNBOX * 2 * BK;          // 4 KB: BK rows of 128 bytes
+constexpr int STAGES = BK == 64 ? 2 : 4;
+constexpr int A_TILE_BYTES = BM * BK * 2;            // one part of the A tile: 8 KB
+constexpr int B_HALF_BYTES = 128 * BK * 2;           // one part of one 128-column half: 8 KB
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 4 * B_HALF_BYTES;   // hi + lo of both operands: 48 KB
+// Epilogue staging: every accumulate warp turns its 32 x 32 blocks through shared memory (pitch 33 floats, free
+// of bank conflicts both ways) so that C leaves - and, with beta, enters - as whole 128-byte row pieces.
+constexpr int EPI_PITCH = 33;
+constexpr int EPI_WARP_FLOATS = 32 * EPI_PITCH;
+constexpr int EPI_BYTES = 8 * EPI_WARP_FLOATS * 4;                // EPI_WARPS warps (declared below)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;    // + slack for 1024-byte alignment
 // Tensor-memory accumulation truncates instead of rounding, so a long K loop drifts (measured 3.5e-5 relative
 // at K = 4096).  The K loop is therefore cut into chunks of 64 K values: each chunk accumulates from zero in
 // tensor memory and the epilogue warps add the finished chunk into float32 registers (round-to-nearest).  The
@@ -61,7 +68,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;           // + slack for
 constexpr int LO_SHIFT = 11;
 constexpr int MMA_N = 128;                           // the tile's two column halves take turns (see below)
 constexpr int TMEM_COLS = 2 * BN;                    // 512: per column half a main and a cross accumulator
-constexpr int EPI_WARPS = 8;                         // two per TMEM lane quarter, 64 columns of each half
+constexpr int EPI_WARPS = 8;                         // per column half one warp for each TMEM lane quarter
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
 
 struct GemmKernelParams {
@@ -92,13 +99,30 @@ __host__ __device__ __forceinline__ int scale_exponent(unsigned maxbits) {
 __device__ __forceinline__ float pow2f(int k) { return __uint_as_float((unsigned)(127 + k) << 23); }
 
 // ---- PTX wrappers ---------------------------------------------------------
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
-                                            int c2) {
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(smem_addr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c0), "r"(c1),
-        "r"(c2)
+        "r"(c2), "r"(c3)
         : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_addr(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(c0), "r"(c1),
+        "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+// One copy = both parts (hi then lo) of 128 rows of an operand for one K block: 16 KB.
+template <int MN_MAJOR>
+__device__ __forceinline__ void load_rows128(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int row0, int k0,
+                                             int batch) {
+    if (MN_MAJOR) tma_load_5d(smem_dst, map, bar, 0, k0, row0 / MNBOX, 0, batch);
+    else tma_load_4d(smem_dst, map, bar, k0, row0, 0, batch);
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_holder, uint32_t ncols) {
@@ -122,6 +146,12 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// streaming store: the line is not read again, so it should be the first to leave the L2
+__device__ __forceinline__ void st_global_cs_f4(float* dst, const float4& v) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -165,24 +195,27 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
            ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (layout_type << 61);
 }
 
-// descriptor of the kk-th slice (32 bytes of K: 16 FP16 values) of an operand tile
+// descriptor of the kk-th slice (16 FP16 values of K) of an operand tile
 template <int MN_MAJOR>
 __device__ __forceinline__ uint64_t operand_desc(uint32_t tile_saddr, int kk) {
     if (MN_MAJOR) {
-        // MN-major, 128-byte swizzle (type 2): TMA boxes of 64 K-rows x 64 row-elements (8 KB) placed 8192 B
+        // MN-major, 128-byte swizzle (type 2): TMA boxes of BK K-rows x 64 row-elements (4 KB) placed 4096 B
         // apart along the row index, groups of 8 K-rows 1024 B apart; a K = 16 slice is two groups
-        return smem_desc(tile_saddr + kk * 2048, 8192, 1024, 2);
+        return smem_desc(tile_saddr + kk * 2048, MNBOX_BYTES, 1024, 2);
     }
-    // K-major, 128-byte swizzle (type 2): rows of 128 B (64 halves of K), 8-row groups 1024 B apart; a K = 16
+    // K-major, 64-byte swizzle (type 4): rows of 64 B (32 halves of K), 8-row groups 512 B apart; a K = 16
     // slice starts 32 B further into the row
-    return smem_desc(tile_saddr + kk * 32, 16, 1024, 2);
+    return smem_desc(tile_saddr + kk * 32, 16, 8 * KROW_BYTES, KROW_BYTES == 128 ? 2 : 4);
 }
 
 // Accumulation chunks.  A chunk is KC consecutive K blocks accumulated in tensor memory before the epilogue warps
-// add it to their float32 registers; the chunks of the tile's two column halves are offset by KC/2 blocks, so the
+// add it to their float32 registers.  The chunks of the tile's two column halves are offset by KC/2 blocks, so the
 // halves never finish a chunk at the same K block: the half that starts a new chunk is issued second and its
-// drain hides behind the other half's MMAs.
-__device__ __forceinline__ bool half_starts(int h, int it, int kc) { return it == 0 || (it % kc) == (h ? kc / 2 : 0); }
+// drain hides behind the other half's MMAs.  The first chunk of half 1 is KC + KC/2 blocks long (not KC/2): at
+// the start of a tile the warps that drain are still storing the previous tile.
+__device__ __forceinline__ bool half_starts(int h, int it, int kc) {
+    return it == 0 || (h ? ((it % kc) == kc / 2 && it > kc / 2) : (it % kc) == 0);
+}
 __device__ __forceinline__ bool half_ends(int h, int it, int total, int kc) {
     return it == total - 1 || half_starts(h, it + 1, kc);
 }
@@ -198,8 +231,7 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 
 template <int A_MN, int B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_constant__ CUtensorMap mapA_lo,
-                   const __grid_constant__ CUtensorMap mapB_hi, const __grid_constant__ CUtensorMap mapB_lo,
+gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                    const GemmKernelParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
@@ -212,10 +244,7 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     // running side by side share a B tile in L2.  Barrier phases, stage indices and chunk counters run on across
     // tiles: the copies and MMAs of the next tile start while the epilogue warps still store the previous one.
     const int tiles_mn = p.tiles_m * p.tiles_n;
-    constexpr int BK = 64;                                     // K values per block
-    constexpr int MNBOX = 64;                                  // row elements per MN-major TMA box
-    constexpr int MNBOX_BYTES = MNBOX * BK_BYTES;
-    constexpr int CHUNK_KB = 4;                                // K blocks per accumulation chunk (256 values)
+    constexpr int CHUNK_KB = 256 / BK;                         // K blocks per accumulation chunk (256 values)
     const int kblocks = (p.K + BK - 1) / BK;
     const int total = kblocks * p.kbatches;
 
@@ -226,7 +255,7 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
         }
         for (int h = 0; h < 2; ++h) {
             mbar_init(&acc_full[h], 1);
-            mbar_init(&acc_empty[h], EPI_WARPS);
+            mbar_init(&acc_empty[h], EPI_WARPS / 2);
         }
         failed = 0;
         fence_mbar_init();
@@ -239,55 +268,38 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
     const uint32_t tmem_base = tmem_holder;
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---- TMA producer ----
-            int g = 0;                                   // K blocks copied by this CTA so far
-            bool okp = true;
-            for (int t = blockIdx.x; t < p.ntiles && okp; t += gridDim.x) {
-            const int zb = t / tiles_mn, m0 = ((t % tiles_mn) % p.tiles_m) * BM, n0 = ((t % tiles_mn) / p.tiles_m) * BN;
-            for (int it = 0; it < total; ++it, ++g) {
-                const int s = g % STAGES;
-                const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
-                if (!mbar_wait_bounded(&empty_bar[s], ph ^ 1u, p.status)) { failed = 1; okp = false; break; }
-                const int kb = it % kblocks;
-                const int batch = p.kbatches > 1 ? it / kblocks : zb;
-                const int ba = p.a_batched ? batch : 0, bb = p.b_batched ? batch : 0;
-                uint8_t* st = smem + s * STAGE_BYTES;
-                uint8_t* a_hi = st;
-                uint8_t* a_lo = st + A_TILE_BYTES;
-                uint8_t* b_hi = st + 2 * A_TILE_BYTES;
-                mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
-                const int k0 = kb * BK;
-                if (A_MN) {
-#pragma unroll
-                    for (int i = 0; i < BM / MNBOX; ++i) {
-                        tma_load_3d(a_hi + i * MNBOX_BYTES, &mapA_hi, &full_bar[s], m0 + MNBOX * i, k0, ba);
-                        tma_load_3d(a_lo + i * MNBOX_BYTES, &mapA_lo, &full_bar[s], m0 + MNBOX * i, k0, ba);
-                    }
-                } else {
-                    tma_load_3d(a_hi, &mapA_hi, &full_bar[s], k0, m0, ba);
-                    tma_load_3d(a_lo, &mapA_lo, &full_bar[s], k0, m0, ba);
-                }
-                // B: per 128-column half the hi rows and then the lo rows, so that one N = 256 descriptor covers
-                // [b_hi | b_lo] of a half
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint8_t* bh = b_hi + h * 2 * B_HALF_BYTES;
-                    uint8_t* bl = bh + B_HALF_BYTES;
-                    const int nb = n0 + h * MMA_N;
-                    if (B_MN) {
-#pragma unroll
-                        for (int i = 0; i < MMA_N / MNBOX; ++i) {
-                            tma_load_3d(bh + i * MNBOX_BYTES, &mapB_hi, &full_bar[s], nb + MNBOX * i, k0, bb);
-                            tma_load_3d(bl + i * MNBOX_BYTES, &mapB_lo, &full_bar[s], nb + MNBOX * i, k0, bb);
-                        }
-                    } else {
-                        tma_load_3d(bh, &mapB_hi, &full_bar[s], k0, nb, bb);
-                        tma_load_3d(bl, &mapB_lo, &full_bar[s], k0, nb, bb);
-                    }
-                }
+        // ---- TMA producer.  A stage is three copies: each tensor map covers both parts of its operand, and one
+        // copy brings the hi and lo rows of 128 rows (the A tile; a 128-column half of the B tile).  clock64
+        // stamps around the refill of a stage: the issuing warp is held 600-1000 cycles for the 96 KB of a stage
+        // whether they go as ten copies or as three, from one lane or from several, and the data is complete
+        // about 1500 cycles later - the refill of one stage takes longer than the 1536 tensor-core cycles of the
+        // other, so the kernel runs at the rate the stage data arrives (about 42 bytes per cycle and SM) ----
+        int g = 0;                                       // K blocks copied by this CTA so far
+        bool okp = true;
+        for (int t = blockIdx.x; t < p.ntiles && okp; t += gridDim.x) {
+        const int zb = t / tiles_mn, m0 = ((t % tiles_mn) % p.tiles_m) * BM, n0 = ((t % tiles_mn) / p.tiles_m) * BN;
+        for (int it = 0; it < total; ++it, ++g) {
+            const int s = g % STAGES;
+            const uint32_t ph = (uint32_t)(g / STAGES) & 1u;
+            bool w = true;
+            if (lane == 0) {
+                w = mbar_wait_bounded(&empty_bar[s], ph ^ 1u, p.status);
+                if (!w) failed = 1;
+                else mbar_arrive_expect_tx(&full_bar[s], STAGE_BYTES);
             }
-            }
+            w = __shfl_sync(0xffffffffu, w, 0);          // also orders the copies after the arming of the barrier
+            if (!w) { okp = false; break; }
+            const int kb = it % kblocks;
+            const int batch = p.kbatches > 1 ? it / kblocks : zb;
+            const int ba = p.a_batched ? batch : 0, bb = p.b_batched ? batch : 0;
+            uint8_t* st = smem + s * STAGE_BYTES;
+            const int k0 = kb * BK;
+            // the A tile [a_hi | a_lo], then per 128-column half [b_hi | b_lo] (one N = 256 descriptor covers a half)
+            if (lane == 0) load_rows128<A_MN>(st, &mapA, &full_bar[s], m0, k0, ba);
+            else if (lane < 3)
+                load_rows128<B_MN>(st + 2 * A_TILE_BYTES + (lane - 1) * 2 * B_HALF_BYTES, &mapB, &full_bar[s],
+                                   n0 + (lane - 1) * MMA_N, k0, bb);
+        }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -318,7 +330,7 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
                     // output columns are [main | cross] (one read of a_hi instead of two), then a_lo * b_hi
                     const uint32_t b_hi = st + 2 * A_TILE_BYTES + h * 2 * B_HALF_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < BK_BYTES / 32; ++kk) {
+                    for (int kk = 0; kk < BK / 16; ++kk) {
                         const uint64_t ah = operand_desc<A_MN>(a_hi, kk), al = operand_desc<A_MN>(a_lo, kk);
                         const uint64_t bh = operand_desc<B_MN>(b_hi, kk);
                         const uint32_t acc_flag = (starts && kk == 0) ? 0u : 1u;
@@ -334,77 +346,81 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA_hi, const __grid_con
             }
         }
     } else {
-        // ---- accumulate + epilogue: warps 2..9; TMEM lane quarter = warp % 4, 64-column slice = (warp - 2) / 4 ----
+        // ---- accumulate + epilogue: warps 2..9; TMEM lane quarter = warp % 4, column half = (warp - 2) / 4.
+        // The warps of a half depend on nothing the other half does: they store their half of a finished tile
+        // while the tensor core works on the next one, and only have to be back when the first chunk of their
+        // half of that tile is complete (four K blocks later for half 0, six for half 1).
         const int quarter = warp & 3;
-        const int slice = (warp - 2) >> 2;
-        float acc[2][64];                        // scaled units (FP16 parts): the scales come off once, at the end
+        const int h = (warp - 2) >> 2;
+        float acc[MMA_N];                        // scaled units (FP16 parts): the scales come off once, at the end
         const float cross_scale = pow2f(-LO_SHIFT);
         bool ok = true;
-        int ch0 = 0, ch1 = 0;                            // chunks drained per column half
-        auto drain = [&](auto H, int& chn) {
-            constexpr int h = decltype(H)::value;
-            if (ok) ok = mbar_wait_bounded(&acc_full[h], (uint32_t)chn & 1u, p.status);
-            tc_fence_after();
-            if (ok) {
-                const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 2 * MMA_N + slice * 64);
-#pragma unroll
-                for (int part = 0; part < 4; ++part) {
-                    float vm[16], vc[16];
-                    tmem_ld16_pair(t0 + part * 16, t0 + MMA_N + part * 16, vm, vc);   // hi*hi ; hi*lo + lo*hi
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        acc[h][part * 16 + i] = fmaf(vc[i], cross_scale, acc[h][part * 16 + i] + vm[i]);
-                }
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[h]);            // the issuer may start this half's next chunk
-            ++chn;
-        };
+        int chn = 0;                                     // chunks drained
+        // exact power-of-two scales, applied one after the other (read once: under the load of the operand
+        // copies a global read takes thousands of cycles)
+        const float ua = pow2f(-scale_exponent(*p.amax_a)), ub = pow2f(-scale_exponent(*p.amax_b));
+        float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES) + (warp - 2) * EPI_WARP_FLOATS;
+        const int rsub = lane >> 3, c4 = (lane & 7) * 4;           // coalesced phase: 4 rows x 8 quads per instruction
+        const uint32_t t0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(h * 2 * MMA_N);
         for (int t = blockIdx.x; t < p.ntiles; t += gridDim.x) {
-        const int zb = t / tiles_mn, m0 = ((t % tiles_mn) % p.tiles_m) * BM, n0 = ((t % tiles_mn) / p.tiles_m) * BN;
+            const int zb = t / tiles_mn, m0 = ((t % tiles_mn) % p.tiles_m) * BM, n0 = ((t % tiles_mn) / p.tiles_m) * BN;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[0][i] = acc[1][i] = 0.f;
-        for (int it = 0; it < total; ++it) {
-            const int first = first_half(it, CHUNK_KB);
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                const int h = q == 0 ? first : 1 - first;
+            for (int i = 0; i < MMA_N; ++i) acc[i] = 0.f;
+            for (int it = 0; it < total; ++it) {
                 if (!half_ends(h, it, total, CHUNK_KB)) continue;
-                if (h == 0) drain(std::integral_constant<int, 0>{}, ch0);
-                else drain(std::integral_constant<int, 1>{}, ch1);
-            }
-        }
-        if (ok && !failed) {
-            const int row = m0 + quarter * 32 + lane;
-            // exact power-of-two scales, applied one after the other
-            const float ua = pow2f(-scale_exponent(*p.amax_a)), ub = pow2f(-scale_exponent(*p.amax_b));
-            if (row < p.M) {
+                // a chunk of this half is complete: add it to the registers and hand the columns back
+                if (ok) ok = mbar_wait_bounded(&acc_full[h], (uint32_t)chn & 1u, p.status);
+                tc_fence_after();
+                if (ok) {
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int col0 = n0 + h * MMA_N + slice * 64;
-                    float* crow = p.C + (long long)zb * p.c_batch_stride + (long long)row * p.ldc + col0;
+                    for (int part = 0; part < MMA_N / 16; ++part) {
+                        float vm[16], vc[16];
+                        tmem_ld16_pair(t0 + part * 16, t0 + MMA_N + part * 16, vm, vc);   // hi*hi ; hi*lo + lo*hi
 #pragma unroll
-                    for (int g = 0; g < 16; ++g) {
-                        const int col = col0 + 4 * g;
-                        float* dst = crow + 4 * g;
-                        float4 o = make_float4((acc[h][4 * g] * ua) * ub, (acc[h][4 * g + 1] * ua) * ub,
-                                               (acc[h][4 * g + 2] * ua) * ub, (acc[h][4 * g + 3] * ua) * ub);
-                        if (p.c_vec && col + 3 < p.N) {
-                            if (p.beta) {
-                                const float4 cin = *reinterpret_cast<const float4*>(dst);
-                                o.x += cin.x; o.y += cin.y; o.z += cin.z; o.w += cin.w;
-                            }
-                            *reinterpret_cast<float4*>(dst) = o;
-                        } else {
-                            const float ov[4] = {o.x, o.y, o.z, o.w};
-                            for (int e = 0; e < 4; ++e)
-                                if (col + e < p.N) dst[e] = ov[e] + (p.beta ? dst[e] : 0.f);
-                        }
+                        for (int i = 0; i < 16; ++i)
+                            acc[part * 16 + i] = fmaf(vc[i], cross_scale, acc[part * 16 + i] + vm[i]);
                     }
                 }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[h]);            // the issuer may start this half's next chunk
+                ++chn;
             }
-        }
+            // The 32 x 32 blocks of the warp turn through the staging tile: lane = row on the way in, 4 rows x 128
+            // bytes per instruction on the way out.
+            if (ok && !failed) {
+                float* cbase = p.C + (long long)zb * p.c_batch_stride;
+#pragma unroll
+                for (int blk = 0; blk < MMA_N / 32; ++blk) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) stg[lane * EPI_PITCH + c] = (acc[blk * 32 + c] * ua) * ub;
+                    __syncwarp();
+                    const int col = n0 + h * MMA_N + blk * 32 + c4;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const int rr = 4 * k + rsub;
+                        const int row = m0 + quarter * 32 + rr;
+                        const float* sp = stg + rr * EPI_PITCH + c4;
+                        float4 o = make_float4(sp[0], sp[1], sp[2], sp[3]);
+                        if (row < p.M) {
+                            float* dst = cbase + (long long)row * p.ldc + col;
+                            if (p.c_vec && col + 3 < p.N) {
+                                if (p.beta) {
+                                    const float4 cin = *reinterpret_cast<const float4*>(dst);
+                                    o.x += cin.x; o.y += cin.y; o.z += cin.z; o.w += cin.w;
+                                }
+                                st_global_cs_f4(dst, o);           // written once, not read again by this kernel
+                            } else {
+                                if (col + 0 < p.N) dst[0] = o.x + (p.beta ? dst[0] : 0.f);
+                                if (col + 1 < p.N) dst[1] = o.y + (p.beta ? dst[1] : 0.f);
+                                if (col + 2 < p.N) dst[2] = o.z + (p.beta ? dst[2] : 0.f);
+                                if (col + 3 < p.N) dst[3] = o.w + (p.beta ? dst[3] : 0.f);
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
         }
     }
     tc_fence_before();
@@ -503,33 +519,47 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// Tensor map of one split part (halves): K-major -> dims (K, rows, batch), box (64, box_rows, 1);
-// MN-major -> dims (rows, K, batch), box (64, 64, 1).  Out-of-range elements read as zero.
-int make_map(CUtensorMap* map, const void* base, int mn_major, long long rows, long long K, long long ld,
-             long long batch_stride, int batches, int box_rows) {
+// Tensor map of a split operand (halves), both parts.  `part_stride` is the distance from the hi to the lo part
+// in bytes.  K-major: dims (K, rows, part, batch), box (BK, 128, 2, 1), 64-byte swizzle.  MN-major: dims (64, K,
+// rows / 64, part, batch), box (64, BK, 2, 2, 1), 128-byte swizzle: the row index is cut into the 64-element
+// boxes the MMA descriptors expect, so one copy fills two boxes of each part.  Out-of-range K rows and boxes read
+// as zero; the last box of an MN-major operand may reach up to 63 elements past `rows` (into the next row, or
+// into the slack that split_part_halves() leaves behind the last row) - those values meet only rows or columns
+// of C that are never stored.
+int make_map(CUtensorMap* map, const void* base, long long part_stride, int mn_major, long long rows, long long K,
+             long long ld, long long batch_stride, int batches) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) {
         set_error("cuTensorMapEncodeTiled is not available from the driver");
         return AUSSM_ECUDA;
     }
-    cuuint64_t dims[3], strides[2];
-    cuuint32_t box[3], estr[3] = {1, 1, 1};
-    const cuuint32_t inner = 64;                  // 128 bytes of the contiguous index per box row
-    const cuuint64_t esize = 2;
-    if (mn_major) {
-        dims[0] = (cuuint64_t)rows; dims[1] = (cuuint64_t)K;
-        box[0] = inner; box[1] = inner;           // one K block of rows: 64 x 64 halves
-    } else {
-        dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows;
-        box[0] = inner; box[1] = (cuuint32_t)box_rows;
+    if (part_stride <= 0 || part_stride % 16) {
+        set_error("gemm_split3: the lo part must follow the hi part at a multiple of 16 bytes (distance %lld)",
+                  part_stride);
+        return AUSSM_EINVAL;
     }
-    dims[2] = (cuuint64_t)batches;
-    box[2] = 1;
-    strides[0] = (cuuint64_t)ld * esize;
-    strides[1] = (cuuint64_t)(batches > 1 ? batch_stride : (long long)dims[1] * ld) * esize;
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    cuuint64_t dims[5], strides[4];
+    cuuint32_t box[5], estr[5] = {1, 1, 1, 1, 1};
+    const cuuint64_t esize = 2;
+    const cuuint64_t bstride = (cuuint64_t)(batches > 1 ? batch_stride : 8) * esize;   // unused when batches == 1
+    int rank;
+    if (mn_major) {
+        rank = 5;
+        dims[0] = MNBOX; dims[1] = (cuuint64_t)K; dims[2] = (cuuint64_t)((rows + MNBOX - 1) / MNBOX); dims[3] = 2;
+        dims[4] = (cuuint64_t)batches;
+        box[0] = MNBOX; box[1] = BK; box[2] = 128 / MNBOX; box[3] = 2; box[4] = 1;
+        strides[0] = (cuuint64_t)ld * esize; strides[1] = MNBOX * esize; strides[2] = (cuuint64_t)part_stride;
+        strides[3] = bstride;
+    } else {
+        rank = 4;
+        dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)rows; dims[2] = 2; dims[3] = (cuuint64_t)batches;
+        box[0] = BK; box[1] = 128; box[2] = 2; box[3] = 1;
+        strides[0] = (cuuint64_t)ld * esize; strides[1] = (cuuint64_t)part_stride; strides[2] = bstride;
+    }
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box,
+                    estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    (mn_major || KROW_BYTES == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with code %d (rows=%lld K=%lld ld=%lld batches=%d mn_major=%d)", (int)r,
                   rows, K, ld, batches, mn_major);
@@ -546,7 +576,7 @@ int launch(const CUtensorMap* maps, const GemmKernelParams& kp, dim3 grid, cudaS
         set_error("gemm_split3: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         return AUSSM_ECUDA;
     }
-    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], kp);
+    kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(maps[0], maps[1], kp);
     e = cudaGetLastError();
     if (e != cudaSuccess) {
         set_error("gemm_split3 launch: %s", cudaGetErrorString(e));
@@ -586,13 +616,12 @@ int gemm_split3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
         set_error("gemm_split3: unsupported shape or alignment of the split operands (M=%d N=%d K=%d)", s.M, s.N, s.K);
         return AUSSM_EINVAL;
     }
-    alignas(64) CUtensorMap maps[4];
+    alignas(64) CUtensorMap maps[2];
     const int ab = A.batch_stride != 0 ? s.batches : 1, bb = B.batch_stride != 0 ? s.batches : 1;
-    if (int rc = make_map(&maps[0], A.hi, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
-    if (int rc = make_map(&maps[1], A.lo, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab, BM)) return rc;
-    // K-major B: one part of a 128-column half per copy
-    if (int rc = make_map(&maps[2], B.hi, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, 128)) return rc;
-    if (int rc = make_map(&maps[3], B.lo, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb, 128)) return rc;
+    const long long a_ps = static_cast<const char*>(A.lo) - static_cast<const char*>(A.hi);
+    const long long b_ps = static_cast<const char*>(B.lo) - static_cast<const char*>(B.hi);
+    if (int rc = make_map(&maps[0], A.hi, a_ps, A.mn_major, s.M, s.K, A.ld, A.batch_stride, ab)) return rc;
+    if (int rc = make_map(&maps[1], B.hi, b_ps, B.mn_major, s.N, s.K, B.ld, B.batch_stride, bb)) return rc;
     GemmKernelParams kp;
     kp.C = C; kp.ldc = s.ldc; kp.c_batch_stride = s.c_batch_stride;
     kp.M = s.M; kp.N = s.N; kp.K = s.K;

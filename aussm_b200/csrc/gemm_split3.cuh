@@ -35,6 +35,11 @@ struct GemmShape {
     long long c_batch_stride;
 };
 
+// Halves to reserve for one part of a split operand that holds `halves` values: rounded up to 256 bytes, with
+// room for the up to 63 halves that the last copy of an MN-major operand reads past the end of its last row.
+// The lo part must follow the hi part (one tensor map covers both).
+inline size_t split_part_halves(size_t halves) { return (halves + 64 + 127) / 128 * 128; }
+
 // C[m][n] (+)= sum_k A(m,k) B(n,k).  Returns 0 or a negative AUSSM_E* code.
 int gemm_split3(const SplitOperand& A, const SplitOperand& B, float* C, const GemmShape& s, cudaStream_t stream);
 

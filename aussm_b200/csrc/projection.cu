@@ -14,7 +14,8 @@ size_t up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 size_t proj_scratch_bytes(int B, int D, long long M_, long long ldw) {
     const size_t M = (size_t)M_, Dp = up((size_t)D, 8);
-    const size_t halves = 2 * up(M * Dp, 128) + 2 * up((size_t)B * D * ldw, 128) + 2 * up((size_t)B * M * ldw, 128);
+    const size_t halves = 2 * split_part_halves(M * Dp) + 2 * split_part_halves((size_t)B * D * ldw) +
+                          2 * split_part_halves((size_t)B * M * ldw);
     return halves * 2 + 256;
 }
 
@@ -23,7 +24,7 @@ void proj_scratch_bind(ProjScratch& s, void* base, int B, int D, long long M_, l
     char* p = static_cast<char*>(base);
     auto take = [&](size_t halves) {
         void* r = p;
-        p += up(halves, 128) * 2;          // every part starts 256-byte aligned
+        p += split_part_halves(halves) * 2;          // every part starts 256-byte aligned
         return r;
     };
     s.x_hi = take(M * Dp);
