@@ -692,7 +692,8 @@ def run_e2e(args, dev, world, rank):
             "copy_floor_gb_s_per_rank_each_way": (h2d + d2h) / 2 / (floor_ms * 1e-3) / 1e9,
             "host_cpus_bound": numa_cpus, "gpu_launches_per_step": launches,
             "api": "aussm_b200.HostBatchStep (chunks of batch/8 through ssm_adaptive_interface, the extension_cpp "
-                   "drop-in; three-stream copy-in / compute / copy-out pipeline), host pinned buffers"}
+                   "drop-in; three-stream copy-in / compute / copy-out pipeline: parameters first, forward as soon "
+                   "as u, dt, z are there, y out during the backward pass), host pinned buffers"}
 
 
 def main():
