@@ -39,7 +39,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr int cmaxi(int a, int b) { return a > b ? a : b; }
 constexpr int cmini(int a, int b) { return a < b ? a : b; }
 
-template <int NL_, bool BWD_>
+template <int NL_, bool BWD_, bool REAL_ = false>
 struct CCfg {
     static constexpr int NL = NL_;
     static constexpr int CPW = 32 / NL;
@@ -49,8 +49,10 @@ struct CCfg {
     // ms - its warps drift apart (atomics, long reverse pass) and wait for each other at the two barriers.
     static constexpr int WARPS = (NL >= 8 && !BWD_) ? 4 : 1;
     static constexpr int AUX = BWD_ ? 4 : 3;                      // u, dt, z [, gy]
-    static constexpr int OWN_ROWS = 64;                           // rho rows then theta rows, one per lane
-    static constexpr int BC_ROWS = 4 * NL;                        // B_re, B_im, C_re, C_im
+    static constexpr bool REAL = REAL_;                           // no theta rows, no imaginary B / C rows
+    static constexpr int OWN_ROWS = REAL_ ? 32 : 64;              // rho rows then theta rows, one per lane
+    static constexpr int BC_ROWS = (REAL_ ? 2 : 4) * NL;          // B_re, B_im, C_re, C_im (real: B_re, C_re)
+    static constexpr int CROW = REAL_ ? 1 : 2;                    // block of the tile that holds C_re
     static constexpr int STAGE_FLOATS = OWN_ROWS * TP + CPW * AUX * T;      // per warp
     static constexpr int BC_FLOATS = BC_ROWS * TP;                          // per block
     // not staged.  forward: s row + p tile.  backward: s, w, d silu(u)/du rows + the tiles of the two column sums
@@ -94,7 +96,7 @@ struct CMap {
             const int row = id / NQ, col = id % NQ;
             bc_ptr[i] = nullptr;
             if (row < C::BC_ROWS) {
-                const int which = row / C::NL, j = row % C::NL;
+                const int which = (C::REAL ? 2 : 1) * (row / C::NL), j = row % C::NL;
                 const float* base = bc_src[which];
                 bc_ptr[i] = base ? base + (long long)(j < N ? j : 0) * ld_row + col * 4 : nullptr;
             }
@@ -167,9 +169,11 @@ __device__ __forceinline__ void lambda4(const float4 r4, const float4 t4, float 
 // ---------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------
-template <int NL>
+// REAL: no angle stream and real B, C - the state, the multiplier and every product are real (the positive-real
+// operator); the imaginary halves of the arithmetic and the sine / cosine are compiled out.
+template <int NL, bool REAL>
 __global__ void __launch_bounds__(CCfg<NL, false>::WARPS * 32) cplx_fwd_kernel(const CplxFwdParams p) {
-    using C = CCfg<NL, false>;
+    using C = CCfg<NL, false, REAL>;
     constexpr int CPW = C::CPW, AUX = C::AUX, VW = C::VW;
     extern __shared__ __align__(128) float smem_all[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -255,22 +259,32 @@ __global__ void __launch_bounds__(CCfg<NL, false>::WARPS * 32) cplx_fwd_kernel(c
         auto quad = [&](const int q) {
             const float4 s4 = ld_shared_f4(srow + c * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
-            const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
-            const float4 cr4 = ld_shared_f4(bc + (2 * NL + j) * TP + 4 * q);
-            const float4 ci4 = ld_shared_f4(bc + (3 * NL + j) * TP + 4 * q);
-            float lr[4], li[4];
-            lambda4(ld_shared_f4(st + lane * TP + 4 * q), ld_shared_f4(st + (32 + lane) * TP + 4 * q), lr, li);
+            const float4 cr4 = ld_shared_f4(bc + (C::CROW * NL + j) * TP + 4 * q);
             const float sv[4] = AUSSM_F4(s4);
-            const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
-            const float crv[4] = AUSSM_F4(cr4), civ[4] = AUSSM_F4(ci4);
+            const float brv[4] = AUSSM_F4(br4), crv[4] = AUSSM_F4(cr4);
             float pv[4];
+            if (REAL) {
+                const float4 r4 = ld_shared_f4(st + lane * TP + 4 * q);
+                const float rv[4] = AUSSM_F4(r4);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float nr = fmaf(lr[e], hr, fmaf(-li[e], hi, sv[e] * brv[e]));
-                const float ni = fmaf(lr[e], hi, fmaf(li[e], hr, sv[e] * biv[e]));
-                hr = nr;
-                hi = ni;
-                pv[e] = act ? fmaf(crv[e], nr, -civ[e] * ni) : 0.f;
+                for (int e = 0; e < 4; ++e) {
+                    hr = fmaf(ex2_ftz(rv[e] * kLog2e), hr, sv[e] * brv[e]);
+                    pv[e] = act ? crv[e] * hr : 0.f;
+                }
+            } else {
+                const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
+                const float4 ci4 = ld_shared_f4(bc + (3 * NL + j) * TP + 4 * q);
+                float lr[4], li[4];
+                lambda4(ld_shared_f4(st + lane * TP + 4 * q), ld_shared_f4(st + (32 + lane) * TP + 4 * q), lr, li);
+                const float biv[4] = AUSSM_F4(bi4), civ[4] = AUSSM_F4(ci4);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float nr = fmaf(lr[e], hr, fmaf(-li[e], hi, sv[e] * brv[e]));
+                    const float ni = fmaf(lr[e], hi, fmaf(li[e], hr, sv[e] * biv[e]));
+                    hr = nr;
+                    hi = ni;
+                    pv[e] = act ? fmaf(crv[e], nr, -civ[e] * ni) : 0.f;
+                }
             }
             st_shared_f4(pt + lane * TP + 4 * q, make_float4(pv[0], pv[1], pv[2], pv[3]));
         };
@@ -320,10 +334,10 @@ __device__ __forceinline__ void red_add_v4c(float* addr, const float (&v)[4]) {
                  : "memory");
 }
 
-template <int NL>
+template <int NL, bool REAL>
 __global__ void __launch_bounds__(CCfg<NL, true>::WARPS * 32)
 cplx_bwd_kernel(const CplxBwdParams p) {
-    using C = CCfg<NL, true>;
+    using C = CCfg<NL, true, REAL>;
     constexpr int CPW = C::CPW, AUX = C::AUX, VW = C::VW;
     extern __shared__ __align__(128) float smem_all[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -431,19 +445,33 @@ cplx_bwd_kernel(const CplxBwdParams p) {
 
         // recompute the tile's states: lambda replaces (rho, theta) in the stage, the state before each step
         // stays in registers (the quads of a tile are unrolled, so the arrays are indexed statically)
-        float hpr[T], hpi[T];
+        float hpr[T], hpi[REAL ? 1 : T];
         auto recompute = [&](const int q) {
             const float4 s4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
+            const float sv[4] = AUSSM_F4(s4);
+            const float brv[4] = AUSSM_F4(br4);
+            if (REAL) {
+                const float4 r4 = ld_shared_f4(st + lane * TP + 4 * q);
+                const float rv[4] = AUSSM_F4(r4);
+                float lr[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    lr[e] = ex2_ftz(rv[e] * kLog2e);
+                    hpr[4 * q + e] = hr;
+                    hr = fmaf(lr[e], hr, sv[e] * brv[e]);
+                }
+                st_shared_f4(st + lane * TP + 4 * q, make_float4(lr[0], lr[1], lr[2], lr[3]));
+                return;
+            }
             const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
             float lr[4], li[4];
             lambda4(ld_shared_f4(st + lane * TP + 4 * q), ld_shared_f4(st + (32 + lane) * TP + 4 * q), lr, li);
-            const float sv[4] = AUSSM_F4(s4);
-            const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
+            const float biv[4] = AUSSM_F4(bi4);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 hpr[4 * q + e] = hr;
-                hpi[4 * q + e] = hi;
+                hpi[REAL ? 0 : 4 * q + e] = hi;
                 const float nr = fmaf(lr[e], hr, fmaf(-li[e], hi, sv[e] * brv[e]));
                 const float ni = fmaf(lr[e], hi, fmaf(li[e], hr, sv[e] * biv[e]));
                 hr = nr;
@@ -452,13 +480,53 @@ cplx_bwd_kernel(const CplxBwdParams p) {
             st_shared_f4(st + lane * TP + 4 * q, make_float4(lr[0], lr[1], lr[2], lr[3]));
             st_shared_f4(st + (32 + lane) * TP + 4 * q, make_float4(li[0], li[1], li[2], li[3]));
         };
+        // reverse pass of the real operator: eta, lambda, the states and every product are real
+        auto reverse_real = [&](const int q) {
+            const float4 s4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
+            const float4 w4 = ld_shared_f4(rows + (c * 3 + 1) * T + 4 * q);
+            const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
+            const float4 cr4 = ld_shared_f4(bc + (C::CROW * NL + j) * TP + 4 * q);
+            const float4 lr4 = ld_shared_f4(st + lane * TP + 4 * q);
+            const float sv[4] = AUSSM_F4(s4), wv[4] = AUSSM_F4(w4);
+            const float brv[4] = AUSSM_F4(br4), crv[4] = AUSSM_F4(cr4), lr[4] = AUSSM_F4(lr4);
+            const float prv[4] = {hpr[4 * q], hpr[4 * q + 1], hpr[4 * q + 2], hpr[4 * q + 3]};
+            float dr[4], E[4], P[4], gBr[4], gCr[4];
+#pragma unroll
+            for (int e = 3; e >= 0; --e) {
+                const float ar = lr[e] * prv[e];                  // a = lambda h_{t-1};  h_t = a + s B
+                const float htr = fmaf(sv[e], brv[e], ar);
+                const float nr = fmaf(crv[e], wv[e], er);         // eta_t = carry + C w
+                dr[e] = nr * ar;
+                E[e] = act ? nr * brv[e] : 0.f;
+                P[e] = act ? crv[e] * htr : 0.f;
+                gBr[e] = act ? nr * sv[e] : 0.f;
+                gCr[e] = act ? wv[e] * htr : 0.f;
+                er = lr[e] * nr;
+            }
+            st_shared_f4(st + lane * TP + 4 * q, make_float4(dr[0], dr[1], dr[2], dr[3]));
+            st_shared_f4(et + lane * TP + 4 * q, make_float4(E[0], E[1], E[2], E[3]));
+            st_shared_f4(pt + lane * TP + 4 * q, make_float4(P[0], P[1], P[2], P[3]));
+#pragma unroll
+            for (int off = NL; off < 32; off <<= 1) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    gBr[e] += __shfl_xor_sync(0xffffffffu, gBr[e], off);
+                    gCr[e] += __shfl_xor_sync(0xffffffffu, gCr[e], off);
+                }
+            }
+            if (c == 0 && j < N && nvalid > 0) {
+                const long long o = bo + (long long)j * p.ld_row + t0 + 4 * q;
+                red_add_v4c(p.dB_re + o, gBr);
+                red_add_v4c(p.dC_re + o, gCr);
+            }
+        };
         // reverse pass
         auto reverse = [&](const int q) {
             const float4 s4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
             const float4 w4 = ld_shared_f4(rows + (c * 3 + 1) * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
             const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
-            const float4 cr4 = ld_shared_f4(bc + (2 * NL + j) * TP + 4 * q);
+            const float4 cr4 = ld_shared_f4(bc + (C::CROW * NL + j) * TP + 4 * q);
             const float4 ci4 = ld_shared_f4(bc + (3 * NL + j) * TP + 4 * q);
             const float4 lr4 = ld_shared_f4(st + lane * TP + 4 * q);
             const float4 li4 = ld_shared_f4(st + (32 + lane) * TP + 4 * q);
@@ -467,7 +535,8 @@ cplx_bwd_kernel(const CplxBwdParams p) {
             const float crv[4] = AUSSM_F4(cr4), civ[4] = AUSSM_F4(ci4);
             const float lr[4] = AUSSM_F4(lr4), li[4] = AUSSM_F4(li4);
             const float prv[4] = {hpr[4 * q], hpr[4 * q + 1], hpr[4 * q + 2], hpr[4 * q + 3]};
-            const float piv[4] = {hpi[4 * q], hpi[4 * q + 1], hpi[4 * q + 2], hpi[4 * q + 3]};
+            const float piv[4] = {hpi[REAL ? 0 : 4 * q], hpi[REAL ? 0 : 4 * q + 1], hpi[REAL ? 0 : 4 * q + 2],
+                                  hpi[REAL ? 0 : 4 * q + 3]};
             float dr[4], dth[4], E[4], P[4], gBr[4], gBi[4], gCr[4], gCi[4];
 #pragma unroll
             for (int e = 3; e >= 0; --e) {
@@ -523,8 +592,12 @@ cplx_bwd_kernel(const CplxBwdParams p) {
         for (int q = 0; q < NQ; ++q)
             if (q < nq) recompute(q);
 #pragma unroll
-        for (int q = NQ - 1; q >= 0; --q)
-            if (q < nq) reverse(q);
+        for (int q = NQ - 1; q >= 0; --q) {
+            if (q < nq) {
+                if (REAL) reverse_real(q);
+                else reverse(q);
+            }
+        }
         // the gradient of the recorded state at this tile's start joins the carry
         if (grec) {
             const float2 g = grec[tile];
@@ -617,9 +690,9 @@ __global__ void __launch_bounds__(256) cplx_reduce_D_kernel(const float* part_D,
     dD[i] = acc;
 }
 
-template <int NL, bool BWD, class Kern, class Params>
+template <int NL, bool BWD, bool REAL, class Kern, class Params>
 cudaError_t launch_nl(Kern kern, const Params& p, cudaStream_t stream) {
-    using C = CCfg<NL, BWD>;
+    using C = CCfg<NL, BWD, REAL>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     const long long tasks = (p.Dmod + C::CPW - 1) / C::CPW;
@@ -633,19 +706,33 @@ cudaError_t launch_nl(Kern kern, const Params& p, cudaStream_t stream) {
 
 cudaError_t launch_cplx_fwd(const CplxFwdParams& p, cudaStream_t stream) {
     if (p.nch <= 0 || p.L <= 0) return cudaSuccess;
-    if (p.N <= 4) return launch_nl<4, false>(cplx_fwd_kernel<4>, p, stream);
-    if (p.N <= 8) return launch_nl<8, false>(cplx_fwd_kernel<8>, p, stream);
-    if (p.N <= 16) return launch_nl<16, false>(cplx_fwd_kernel<16>, p, stream);
-    if (p.N <= 32) return launch_nl<32, false>(cplx_fwd_kernel<32>, p, stream);
+    if (!p.theta && !p.B_im && !p.C_im) {          // everything real
+        if (p.N <= 4) return launch_nl<4, false, true>(cplx_fwd_kernel<4, true>, p, stream);
+        if (p.N <= 8) return launch_nl<8, false, true>(cplx_fwd_kernel<8, true>, p, stream);
+        if (p.N <= 16) return launch_nl<16, false, true>(cplx_fwd_kernel<16, true>, p, stream);
+        if (p.N <= 32) return launch_nl<32, false, true>(cplx_fwd_kernel<32, true>, p, stream);
+        return cudaErrorInvalidValue;
+    }
+    if (p.N <= 4) return launch_nl<4, false, false>(cplx_fwd_kernel<4, false>, p, stream);
+    if (p.N <= 8) return launch_nl<8, false, false>(cplx_fwd_kernel<8, false>, p, stream);
+    if (p.N <= 16) return launch_nl<16, false, false>(cplx_fwd_kernel<16, false>, p, stream);
+    if (p.N <= 32) return launch_nl<32, false, false>(cplx_fwd_kernel<32, false>, p, stream);
     return cudaErrorInvalidValue;
 }
 
 cudaError_t launch_cplx_bwd(const CplxBwdParams& p, cudaStream_t stream) {
     if (p.nch <= 0 || p.L <= 0) return cudaSuccess;
-    if (p.N <= 4) return launch_nl<4, true>(cplx_bwd_kernel<4>, p, stream);
-    if (p.N <= 8) return launch_nl<8, true>(cplx_bwd_kernel<8>, p, stream);
-    if (p.N <= 16) return launch_nl<16, true>(cplx_bwd_kernel<16>, p, stream);
-    if (p.N <= 32) return launch_nl<32, true>(cplx_bwd_kernel<32>, p, stream);
+    if (!p.theta && !p.B_im && !p.C_im && !p.dB_im && !p.dC_im) {
+        if (p.N <= 4) return launch_nl<4, true, true>(cplx_bwd_kernel<4, true>, p, stream);
+        if (p.N <= 8) return launch_nl<8, true, true>(cplx_bwd_kernel<8, true>, p, stream);
+        if (p.N <= 16) return launch_nl<16, true, true>(cplx_bwd_kernel<16, true>, p, stream);
+        if (p.N <= 32) return launch_nl<32, true, true>(cplx_bwd_kernel<32, true>, p, stream);
+        return cudaErrorInvalidValue;
+    }
+    if (p.N <= 4) return launch_nl<4, true, false>(cplx_bwd_kernel<4, false>, p, stream);
+    if (p.N <= 8) return launch_nl<8, true, false>(cplx_bwd_kernel<8, false>, p, stream);
+    if (p.N <= 16) return launch_nl<16, true, false>(cplx_bwd_kernel<16, false>, p, stream);
+    if (p.N <= 32) return launch_nl<32, true, false>(cplx_bwd_kernel<32, false>, p, stream);
     return cudaErrorInvalidValue;
 }
 
