@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaussm_b200.so")
-SOURCES = ["scan_unitary.cu", "projection.cu", "gemm_split3.cu", "scan_s6.cu", "scan_complex.cu", "api.cu", "api_s6.cu", "api_complex.cu", "noalloc.cu", "block_stages.cu"]
+SOURCES = ["scan_unitary.cu", "projection.cu", "gemm_split3.cu", "scan_s6.cu", "scan_s6_wide.cu", "scan_complex.cu", "api.cu", "api_s6.cu", "api_complex.cu", "noalloc.cu", "block_stages.cu"]
 HEADERS = ["common.cuh", "scan_unitary.cuh", "projection.cuh", "gemm_split3.cuh", "host_common.cuh", "scan_s6.cuh", "scan_complex.cuh", os.path.join("..", "..", "include", "aussm_b200.h")]
 
 

@@ -40,7 +40,7 @@ extern "C" {
 
 size_t aussm_b200_selective_scan_ckpt_floats(int B, int D, int N, int L) {
     if (B <= 0 || D <= 0 || N <= 0 || L <= 0) return 0;
-    return (size_t)B * D * N * (size_t)s6_ntiles(L);
+    return (size_t)B * D * N * (size_t)s6_ntiles(L, N);
 }
 
 size_t aussm_b200_selective_scan_bwd_workspace_bytes(int B, int D, int N, int L) {
@@ -66,7 +66,7 @@ int aussm_b200_selective_scan_fwd(const float* u, const float* delta, const floa
     p.u = u; p.delta = delta; p.A = A; p.Bm = Bm; p.Cm = Cm; p.Dskip = Dskip; p.z = z; p.delta_bias = delta_bias;
     p.out = out; p.ckpt = ckpt; p.last_state = last_state; p.delta_softplus = delta_softplus;
     p.nch = B * D; p.Dmod = D; p.N = N; p.L = L;
-    cudaError_t e = launch_s6_fwd(p, (cudaStream_t)stream);
+    cudaError_t e = s6_wide(N) ? launch_s6_wide_fwd(p, (cudaStream_t)stream) : launch_s6_fwd(p, (cudaStream_t)stream);
     if (e != cudaSuccess) {
         set_error("selective_scan_fwd launch: %s", cudaGetErrorString(e));
         return AUSSM_ECUDA;
@@ -112,7 +112,7 @@ int aussm_b200_selective_scan_bwd(const float* gout, const float* u, const float
     p.delta_bias = delta_bias; p.ckpt = ckpt; p.du = du; p.ddelta = ddelta; p.dz = dz; p.dB = dB; p.dC = dC;
     p.part_A = part_A; p.part_D = part_D; p.part_bias = part_bias; p.delta_softplus = delta_softplus;
     p.nch = (int)nch; p.Dmod = D; p.N = N; p.L = L;
-    e = launch_s6_bwd(p, stream);
+    e = s6_wide(N) ? launch_s6_wide_bwd(p, stream) : launch_s6_bwd(p, stream);
     if (e != cudaSuccess) {
         set_error("selective_scan_bwd launch: %s", cudaGetErrorString(e));
         return AUSSM_ECUDA;

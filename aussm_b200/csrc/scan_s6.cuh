@@ -12,6 +12,9 @@
 namespace aussm {
 
 constexpr int kS6Tile = 32;      // steps per tile; the forward pass stores the state at every tile start
+// Channel-per-thread kernels (scan_s6_wide.cu) serve N <= kS6WideStates: 16-step tiles, record (nch, tiles, N)
+constexpr int kS6WideTile = 16;
+constexpr int kS6WideStates = 16;
 
 struct S6FwdParams {
     const float* u;           // (nch, L)
@@ -23,7 +26,8 @@ struct S6FwdParams {
     const float* z;           // (nch, L) or nullptr
     const float* delta_bias;  // (D,) or nullptr
     float* out;               // (nch, L)
-    float* ckpt;              // (nch, N, ntiles): state at the start of every tile, or nullptr
+    float* ckpt;              // state at the start of every tile, or nullptr: (nch, N, tiles of 32 steps) for
+                              // N > 16, (nch, tiles of 16 steps, N) for N <= 16
     float* last_state;        // (nch, N) or nullptr
     int delta_softplus;
     int nch, Dmod, N, L;
@@ -62,10 +66,18 @@ struct S6ReduceParams {
     int batch, D, N;
 };
 
-inline long long s6_ntiles(long long L) { return (L + kS6Tile - 1) / kS6Tile; }
+inline bool s6_wide(int N) { return N <= kS6WideStates; }
+// tiles of the state record (its size is nch * N * tiles floats in both layouts)
+inline long long s6_ntiles(long long L, int N) {
+    const int t = s6_wide(N) ? kS6WideTile : kS6Tile;
+    return (L + t - 1) / t;
+}
 
 cudaError_t launch_s6_fwd(const S6FwdParams& p, cudaStream_t stream);
 cudaError_t launch_s6_bwd(const S6BwdParams& p, cudaStream_t stream);
 cudaError_t launch_s6_reduce(const S6ReduceParams& p, cudaStream_t stream);
+// N <= kS6WideStates
+cudaError_t launch_s6_wide_fwd(const S6FwdParams& p, cudaStream_t stream);
+cudaError_t launch_s6_wide_bwd(const S6BwdParams& p, cudaStream_t stream);
 
 }  // namespace aussm
