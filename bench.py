@@ -392,7 +392,8 @@ def variant_case(kind, b, d, n, l, steps, warmup=3, seed=7):
         Bm, Cm = r(b, n, l) * sc, r(b, n, l) * sc
         leaves = [u, dt, z]
         fwd = lambda: selective_scan_fn(u, dt, A, Bm, Cm, D, z=z, delta_softplus=True)
-        bytes_f, bytes_b, bound = 16, 28, "shared-memory pipe (0.73 / 0.81 busy: profiles/scan_s6_small.md), not HBM"
+        bytes_f, bytes_b, bound = 16, 28, ("instruction issue and dependent-chain latency (issue slots 0.44 / 0.41 busy, shared-memory "
+                                          "pipe 0.62 / 0.60: profiles/scan_s6_small.md), not HBM")
     else:
         raise ValueError(kind)
     ms_f = _time_events(lambda: fwd(), steps, warmup)
