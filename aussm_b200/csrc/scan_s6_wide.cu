@@ -504,10 +504,7 @@ int lanes_per_channel(long long batches, int D, int NS, bool bwd) {
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     auto warps = [&](int lpc) { return batches * ((D + 32 / lpc - 1) / (32 / lpc)); };
-    if (bwd) {
-        if (NS < 2) return 1;
-        return (NS >= 4 && warps(2) < 4LL * sms) ? 4 : 2;
-    }
+    if (bwd) return warps(2) < 4LL * sms ? 4 : 2;
     int lpc = 1;
     while (lpc < 4 && lpc * 2 <= NS && warps(lpc) < 12LL * sms) lpc *= 2;
     return lpc;
@@ -548,11 +545,8 @@ cudaError_t launch_w_fwd_ns(const S6FwdParams& p, cudaStream_t stream) {
 
 template <int NS>
 cudaError_t launch_w_bwd_ns(const S6BwdParams& p, cudaStream_t stream) {
-    switch (lanes_per_channel(p.nch / p.Dmod, p.Dmod, NS, true)) {
-        case 4: return launch_w_bwd<NS, 4>(p, stream);
-        case 2: return launch_w_bwd<NS, 2>(p, stream);
-        default: return launch_w_bwd<NS, 1>(p, stream);
-    }
+    if (lanes_per_channel(p.nch / p.Dmod, p.Dmod, NS, true) == 4) return launch_w_bwd<NS, 4>(p, stream);
+    return launch_w_bwd<NS, 2>(p, stream);
 }
 
 }  // namespace

@@ -247,8 +247,9 @@ int aussm_b200_unitary_bwd_kept(const float* grad_y, const float* gh1_re, const 
  *   out = (sum_j Cm[b][j][t] h_t + Dskip[i] u) * silu(z)        (Dskip, z, delta_bias may be NULL)
  * u, delta, z, out: (B, D, L); A: (D, N); Bm, Cm: (B, N, L).  L must be a
  * multiple of 4 and N <= 32.  `ckpt` (aussm_b200_selective_scan_ckpt_floats
- * floats) receives the state at every 32nd step and is what the backward pass
- * restarts from (NULL when no backward pass will follow).  dB and dC are summed
+ * floats; its layout belongs to the library) receives the state at every 16th
+ * step (every 32nd for N > 16) and is what the backward pass restarts from
+ * (NULL when no backward pass will follow).  dB and dC are summed
  * over the channels with float atomics (as in mamba-ssm), so they are
  * reproducible only up to rounding; everything else is deterministic. */
 size_t aussm_b200_selective_scan_ckpt_floats(int B, int D, int N, int L);
