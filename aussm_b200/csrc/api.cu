@@ -439,7 +439,7 @@ int aussm_b200_gemm_split3_strided(const float* A, int a_mn_major, long long lda
         return rc;
     const SplitOperand sa = {a_hi, a_lo, a_mn_major, a.pitch, a_batched ? a.rows * a.pitch : 0, amax + 0};
     const SplitOperand sb = {b_hi, b_lo, b_mn_major, b.pitch, b_batched ? b.rows * b.pitch : 0, amax + 1};
-    const GemmShape shape = {M, N, K, batches, reduce_batches, beta, ldc, reduce_batches ? 0 : c_batch_stride};
+    const GemmShape shape = {M, N, K, batches, reduce_batches ? 1 : 0, beta, ldc, reduce_batches ? 0 : c_batch_stride};
     return gemm_split3(sa, sb, C, shape, stream);
 }
 

@@ -290,7 +290,7 @@ gemm_split3_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_consta
             w = __shfl_sync(0xffffffffu, w, 0);          // also orders the copies after the arming of the barrier
             if (!w) { okp = false; break; }
             const int kb = it % kblocks;
-            const int batch = p.kbatches > 1 ? it / kblocks : zb;
+            const int batch = zb * p.kbatches + it / kblocks;
             const int ba = p.a_batched ? batch : 0, bb = p.b_batched ? batch : 0;
             uint8_t* st = smem + s * STAGE_BYTES;
             const int k0 = kb * BK;
@@ -604,6 +604,7 @@ int sm_count() {
 
 bool gemm_split3_supported(const SplitOperand& A, const SplitOperand& B, const float* C, const GemmShape& s) {
     if (s.M <= 0 || s.N <= 0 || s.K <= 0 || s.batches <= 0 || !C) return false;
+    if (s.reduce_batches < 0 || (s.reduce_batches > 0 && s.batches % s.reduce_batches)) return false;
     if (!A.amax || !B.amax) return false;
     // the parts are rows of halves whose pitch is a multiple of 16 bytes (split_f16 writes them that way)
     if (A.ld % 8 || B.ld % 8 || A.batch_stride % 8 || B.batch_stride % 8) return false;
@@ -625,7 +626,7 @@ int gemm_split3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
     GemmKernelParams kp;
     kp.C = C; kp.ldc = s.ldc; kp.c_batch_stride = s.c_batch_stride;
     kp.M = s.M; kp.N = s.N; kp.K = s.K;
-    kp.kbatches = s.reduce_batches ? s.batches : 1;
+    kp.kbatches = s.reduce_batches ? s.batches / s.reduce_batches : 1;
     kp.beta = s.beta;
     kp.a_batched = A.batch_stride != 0;
     kp.b_batched = B.batch_stride != 0;
@@ -639,7 +640,7 @@ int gemm_split3(const SplitOperand& A, const SplitOperand& B, float* C, const Ge
     }
     kp.tiles_m = (s.M + BM - 1) / BM;
     kp.tiles_n = (s.N + BN - 1) / BN;
-    kp.ntiles = kp.tiles_m * kp.tiles_n * (s.reduce_batches ? 1 : s.batches);
+    kp.ntiles = kp.tiles_m * kp.tiles_n * (s.reduce_batches ? s.reduce_batches : s.batches);
     const dim3 grid((unsigned)std::min(kp.ntiles, sm_count()), 1, 1);     // one persistent CTA per SM
     if (A.mn_major) return B.mn_major ? launch<1, 1>(maps, kp, grid, stream) : launch<1, 0>(maps, kp, grid, stream);
     return B.mn_major ? launch<0, 1>(maps, kp, grid, stream) : launch<0, 0>(maps, kp, grid, stream);

@@ -29,7 +29,8 @@ struct SplitOperand {
 struct GemmShape {
     int M, N, K;
     int batches;          // number of operand batch entries
-    int reduce_batches;   // 1: C = sum over batches (one output); 0: one output per batch entry
+    int reduce_batches;   // 0: one output per batch entry; g >= 1: the batch entries are summed in g groups of
+                          // batches / g consecutive entries, one output per group (g = 1: C = sum over all)
     int beta;             // 0: overwrite C, 1: add to C
     long long ldc;        // floats; any value (rows that are not 16-byte aligned take scalar stores)
     long long c_batch_stride;

@@ -36,6 +36,7 @@ struct ProjScratch {
     void* u_lo;
     void* dth_hi;     // (B, M, ldw)      window of dtheta
     void* dth_lo;
+    float* dx_part;   // (2, M, D)        partial sums of dx when the batch is summed in two groups
     unsigned* amax;   // bit patterns of max|x|, max|u window|, max|dtheta window|
     long long Dp;
 };
