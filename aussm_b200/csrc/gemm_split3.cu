@@ -55,7 +55,8 @@ constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 4 * B_HALF_BYTES;   // hi + lo of
 // of bank conflicts both ways) so that C leaves - and, with beta, enters - as whole 128-byte row pieces.
 constexpr int EPI_PITCH = 33;
 constexpr int EPI_WARP_FLOATS = 32 * EPI_PITCH;
-constexpr int EPI_BYTES = 8 * EPI_WARP_FLOATS * 4;                // EPI_WARPS warps (declared below)
+constexpr int EPI_WARPS = 8;                         // per column half one warp for each TMEM lane quarter
+constexpr int EPI_BYTES = EPI_WARPS * EPI_WARP_FLOATS * 4;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;    // + slack for 1024-byte alignment
 // Tensor-memory accumulation truncates instead of rounding, so a long K loop drifts (measured 3.5e-5 relative
 // at K = 4096).  The K loop is therefore cut into chunks of 64 K values: each chunk accumulates from zero in
@@ -68,7 +69,6 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + EPI_BYTES;    // + slac
 constexpr int LO_SHIFT = 11;
 constexpr int MMA_N = 128;                           // the tile's two column halves take turns (see below)
 constexpr int TMEM_COLS = 2 * BN;                    // 512: per column half a main and a cross accumulator
-constexpr int EPI_WARPS = 8;                         // per column half one warp for each TMEM lane quarter
 constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
 
 struct GemmKernelParams {

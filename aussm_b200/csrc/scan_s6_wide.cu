@@ -501,8 +501,15 @@ __global__ void __launch_bounds__(32) s6w_bwd_kernel(const S6BwdParams p) {
 // 4096 x 1024: 4.83 / 4.14 / 4.64 ms) - one lane per channel needs every register there is, four repeat the
 // per-channel work of a group four times; four only when even two give less than one warp per scheduler.
 int lanes_per_channel(long long batches, int D, int NS, bool bwd) {
-    int sms = 148, dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    static int sms = 0;                                     // the GPUs of a box are alike
+    if (sms <= 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sms = n;
+        else
+            sms = 148;
+    }
     auto warps = [&](int lpc) { return batches * ((D + 32 / lpc - 1) / (32 / lpc)); };
     if (bwd) return warps(2) < 4LL * sms ? 4 : 2;
     int lpc = 1;

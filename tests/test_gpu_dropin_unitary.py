@@ -166,6 +166,19 @@ def test_host_batch_pipeline_matches_single_call():
             p, q = torch.view_as_real(p), torch.view_as_real(q)
         assert scaled_error(p, q) < 1e-5, k
     assert aussm_b200.device_status() == 0
+    # the same step with the per-chunk record: same results, and a chunk's stages begin and end in order
+    pipe = aussm_b200.HostBatchStep("cuda:0", chunk=2, timeline=True)
+    pipe.step(host_in, out)
+    marks = {}
+    for c, what, ms in pipe.last_timeline():
+        marks.setdefault(c, {})[what] = ms
+    assert torch.equal(out["y"], y0.cpu())
+    assert sorted(k for k in marks if k >= 0) == [0, 1, 2]
+    for c in (0, 1, 2):
+        m = marks[c]
+        assert m["in0"] <= m["in1"] and m["cmp0"] <= m["cmp1"] and m["out0"] <= m["out1"]
+        assert m["in0"] <= m["cmp0"] and m["cmp1"] <= m["out1"]
+    assert marks[-1]["start"] == 0.0 and marks[-1]["end"] >= max(marks[c]["out1"] for c in (0, 1, 2))
 
 
 def test_extension_cpp_shim_and_errors():
