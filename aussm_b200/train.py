@@ -23,7 +23,7 @@ from typing import Iterable, List
 import torch
 import torch.distributed as dist
 
-__all__ = ["shard_range", "allreduce_gradients", "max_over_ranks", "make_config", "train_step"]
+__all__ = ["shard_range", "allreduce_gradients", "max_over_ranks", "make_config", "train_step", "GraphedTrainStep"]
 
 
 def shard_range(total: int, rank: int, world: int):
@@ -149,6 +149,67 @@ def train_step(model, opt, x, y, loss_fn, world: int, micro_batch: int = 0, clip
     torch.nn.utils.clip_grad_norm_(model.parameters(), clip)
     opt.step()
     return total, ncoll
+
+
+class GraphedTrainStep:
+    """One-process training step (forward, backward in micro-batches, clipping, optimizer) of a fixed-shape batch,
+    captured once into a CUDA graph and replayed.
+
+    The small configurations are bound by the host: a step of configuration 3 is several hundred kernels of a few
+    microseconds each, and the Python and launch overhead between them is most of its time.  The operators take
+    their workspaces from the caller's allocator and never synchronise, so the whole step records into one graph.
+    The optimizer must be built with ``capturable=True``.  ``step(x, y)`` copies a new batch of the same shape
+    into the static inputs, replays the graph and returns the loss as a device tensor (reading it synchronises).
+    With more than one rank the gradient all-reduce sits between backward and clipping; that variant is not
+    captured here: use ``train_step``."""
+
+    def __init__(self, model, opt, x, y, loss_fn, micro_batch: int = 0, clip: float = 1.0, global_batch: int = 0,
+                 warmup: int = 3):
+        from . import ops
+        self.model, self.opt, self.loss_fn, self.clip = model, opt, loss_fn, clip
+        self.x, self.y = x.clone(), y.clone()
+        n = x.shape[0]
+        self.gb = global_batch if global_batch > 0 else n
+        self.mb = n if micro_batch <= 0 else min(micro_batch, n)
+        saved = ops.keep_phases
+        if saved == "auto":
+            ops.keep_phases = True          # the free-memory query of "auto" is not a call to make while capturing
+        try:
+            cur = torch.cuda.current_stream()
+            side = torch.cuda.Stream()
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):   # warm-up off the capturing stream: lazy initialisation, allocator state
+                for _ in range(max(1, warmup)):
+                    opt.zero_grad(set_to_none=True)
+                    self._body()
+            cur.wait_stream(side)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            opt.zero_grad(set_to_none=True)
+            with torch.cuda.graph(self.graph):
+                self.loss = self._body()
+        finally:
+            ops.keep_phases = saved
+
+    def _body(self):
+        n = self.x.shape[0]
+        total = torch.zeros((), device=self.x.device)
+        for s in range(0, n, self.mb):
+            out = self.model(self.x[s:s + self.mb])
+            loss = self.loss_fn(out, self.y[s:s + self.mb]) * ((min(s + self.mb, n) - s) / self.gb)
+            loss.backward()
+            total = total + loss.detach()
+        torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.clip, foreach=True)
+        self.opt.step()
+        return total
+
+    def step(self, x=None, y=None):
+        if x is not None:
+            self.x.copy_(x, non_blocking=True)
+        if y is not None:
+            self.y.copy_(y, non_blocking=True)
+        self.graph.replay()
+        return self.loss
 
 
 def main():

@@ -521,9 +521,30 @@ def run_extras(args, dev, world, rank, barrier):
         e1.record()
         barrier()
         ms = max_over_ranks(e0.elapsed_time(e1) / steps, dev, world)
-        train.append({"config": config, "ms_per_step": round(ms, 3), "tokens_per_s": round(tokens / ms * 1e3, 1),
-                      "local_batch": local_batch, "micro_batch": micro, "steps": steps, "warmup": warm,
-                      "allreduce_calls_per_step": ncoll, "loss": loss})
+        rec = {"config": config, "ms_per_step": round(ms, 3), "tokens_per_s": round(tokens / ms * 1e3, 1),
+               "local_batch": local_batch, "micro_batch": micro, "steps": steps, "warmup": warm,
+               "allreduce_calls_per_step": ncoll, "loss": loss}
+        if world == 1 and config == 3:
+            # the same step captured once into a CUDA graph and replayed (the small configuration is bound by the
+            # host's launch rate; one process only: the all-reduce variant is not captured)
+            from aussm_b200.train import GraphedTrainStep
+            model_g, _b, loss_g, _t, _l, _g = make_config(config, dev, rank, world)
+            opt_g = torch.optim.AdamW(model_g.parameters(), lr=1e-3, capturable=True)
+            graphed = GraphedTrainStep(model_g, opt_g, x, y, loss_g, micro_batch=micro, global_batch=gb)
+            for _ in range(warm):
+                graphed.step()
+            torch.cuda.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            for _ in range(steps):
+                gl = graphed.step()
+            g1.record()
+            torch.cuda.synchronize()
+            gms = g0.elapsed_time(g1) / steps
+            rec.update({"ms_per_step_cuda_graph": round(gms, 3),
+                        "tokens_per_s_cuda_graph": round(tokens / gms * 1e3, 1), "loss_cuda_graph": float(gl)})
+            del graphed, model_g, opt_g
+        train.append(rec)
         del model, opt, x, y
         torch.cuda.empty_cache()
     out["training_steps"] = train

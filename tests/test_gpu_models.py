@@ -93,6 +93,38 @@ def test_training_step_runs_and_reduces_the_loss(config):
     assert last < first
 
 
+def test_graphed_training_step_follows_the_eager_one():
+    """The step captured into a CUDA graph and replayed does what the eager step does: same losses step by step (the
+    Mamba layers' dB / dC use float atomics, so equality is up to rounding), and a new batch copied into the static
+    inputs is used."""
+    from aussm_b200.train import GraphedTrainStep
+    dev = torch.device("cuda", 0)
+    model_e, batch, loss_fn, _, _, _ = make_config(3, dev, 0, 1, scale=0.1)
+    model_g, _, _, _, _, _ = make_config(3, dev, 0, 1, scale=0.1)          # same seed: same initial weights
+    x, y = batch()
+    x, y = x[:6], y[:6]
+    x2 = torch.roll(x, 1, 0)
+    opt_e = torch.optim.AdamW(model_e.parameters(), lr=2e-3)
+    opt_g = torch.optim.AdamW(model_g.parameters(), lr=2e-3, capturable=True)
+    for p, q in zip(model_e.parameters(), model_g.parameters()):
+        assert torch.equal(p, q)
+    start = {k: v.clone() for k, v in model_g.state_dict().items()}
+    graphed = GraphedTrainStep(model_g, opt_g, x, y, loss_fn, micro_batch=3, warmup=2)
+    # construction ran warm-up steps on the model: back to the start, optimizer state included
+    model_g.load_state_dict(start)
+    for st in opt_g.state.values():
+        for v in st.values():
+            if torch.is_tensor(v):
+                v.zero_()
+    for xs in (x, x, x2, x2):
+        le, _ = train_step(model_e, opt_e, xs, y, loss_fn, 1, micro_batch=3)
+        lg = float(graphed.step(xs, y))
+        assert abs(le - lg) <= 1e-4 * max(1.0, abs(le)), (le, lg)
+    for p, q in zip(model_e.parameters(), model_g.parameters()):
+        assert torch.allclose(p, q, rtol=1e-3, atol=1e-4)
+    assert aussm_b200.device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(3, 50, 64, 128), (2, 7, 128, 36), (1, 1, 16, 8), (4, 33, 21, 128),
                                    (8, 2048, 64, 256)])
 def test_split_linear_matches_float64(shape, monkeypatch):
