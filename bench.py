@@ -527,28 +527,35 @@ def run_extras(args, dev, world, rank, barrier):
         if world == 1 and config == 3:
             # the same step captured once into a CUDA graph and replayed (the small configuration is bound by the
             # host's launch rate; one process only: the all-reduce variant is not captured)
-            from aussm_b200.train import GraphedTrainStep
-            model_g, _b, loss_g, _t, _l, _g = make_config(config, dev, rank, world)
-            opt_g = torch.optim.AdamW(model_g.parameters(), lr=1e-3, capturable=True)
-            graphed = GraphedTrainStep(model_g, opt_g, x, y, loss_g, micro_batch=micro, global_batch=gb)
-            for _ in range(warm):
-                graphed.step()
-            torch.cuda.synchronize()
-            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            g0.record()
-            for _ in range(steps):
-                gl = graphed.step()
-            g1.record()
-            torch.cuda.synchronize()
-            gms = g0.elapsed_time(g1) / steps
-            rec.update({"ms_per_step_cuda_graph": round(gms, 3),
-                        "tokens_per_s_cuda_graph": round(tokens / gms * 1e3, 1), "loss_cuda_graph": float(gl)})
-            del graphed, model_g, opt_g
+            try:
+                rec.update(_graphed_step(config, dev, x, y, micro, gb, warm, steps, tokens))
+            except Exception as exc:          # the eager figure above stands on its own
+                rec["cuda_graph_error"] = f"{type(exc).__name__}: {exc}"[:300]
         train.append(rec)
         del model, opt, x, y
         torch.cuda.empty_cache()
     out["training_steps"] = train
     return out
+
+
+def _graphed_step(config, dev, x, y, micro, gb, warm, steps, tokens):
+    """The training step of `config` captured once into a CUDA graph and replayed: its time per step."""
+    from aussm_b200.train import GraphedTrainStep, make_config
+    model_g, _b, loss_g, _t, _l, _g = make_config(config, dev, 0, 1)
+    opt_g = torch.optim.AdamW(model_g.parameters(), lr=1e-3, capturable=True)
+    graphed = GraphedTrainStep(model_g, opt_g, x, y, loss_g, micro_batch=micro, global_batch=gb)
+    for _ in range(warm):
+        graphed.step()
+    torch.cuda.synchronize()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(steps):
+        gl = graphed.step()
+    g1.record()
+    torch.cuda.synchronize()
+    gms = g0.elapsed_time(g1) / steps
+    return {"ms_per_step_cuda_graph": round(gms, 3), "tokens_per_s_cuda_graph": round(tokens / gms * 1e3, 1),
+            "loss_cuda_graph": float(gl)}
 
 
 def run_ours(args):
@@ -641,7 +648,13 @@ def run_ours(args):
         e2e = run_e2e(args, dev, world, rank)
     extras = None
     if not args.no_extras:
-        extras = run_extras(args, dev, world, rank, barrier)
+        if world == 1:
+            try:
+                extras = run_extras(args, dev, world, rank, barrier)
+            except Exception as exc:          # the headline line does not depend on the extra configurations
+                extras = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        else:
+            extras = run_extras(args, dev, world, rank, barrier)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu, _ = time_cpu_oracle(d, n, 3, 2, "scan")
