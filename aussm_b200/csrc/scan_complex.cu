@@ -14,11 +14,12 @@
 //
 // Shared memory is what limits the number of resident warps (each state keeps
 // two streams in flight), so the tiles are short (16 steps) and every cell is
-// used several times: the backward kernel's recomputing pass overwrites the
-// rho / theta cells it has consumed with lambda (the reverse pass then needs no
-// second exponential and sine / cosine) and keeps the state before each step in
-// registers; the reverse pass replaces lambda by drho / dtheta, which leave
-// with coalesced stores.  dB and dC (sums over the channels of a
+// used several times: the backward kernel's recomputing pass keeps lambda and
+// the state before each step of the tile in registers (the reverse pass then
+// needs no second exponential and sine / cosine, and no shared-memory round
+// trip: the shared-memory pipe is the busiest unit of this kernel); the reverse
+// pass writes drho / dtheta over the rho / theta cells, which leave with
+// coalesced stores.  dB and dC (sums over the channels of a
 // batch entry) use shuffles and vector float atomics, as the reference's
 // kernels do (ssm_adaptive_complex.cu:358-660).
 #include "scan_complex.cuh"
@@ -446,6 +447,7 @@ cplx_bwd_kernel(const CplxBwdParams p) {
         // recompute the tile's states: lambda replaces (rho, theta) in the stage, the state before each step
         // stays in registers (the quads of a tile are unrolled, so the arrays are indexed statically)
         float hpr[T], hpi[REAL ? 1 : T];
+        float lmr[T], lmi[REAL ? 1 : T];                      // lambda of every step of the tile
         auto recompute = [&](const int q) {
             const float4 s4 = ld_shared_f4(rows + (c * 3 + 0) * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
@@ -459,9 +461,9 @@ cplx_bwd_kernel(const CplxBwdParams p) {
                 for (int e = 0; e < 4; ++e) {
                     lr[e] = ex2_ftz(rv[e] * kLog2e);
                     hpr[4 * q + e] = hr;
+                    lmr[4 * q + e] = lr[e];
                     hr = fmaf(lr[e], hr, sv[e] * brv[e]);
                 }
-                st_shared_f4(st + lane * TP + 4 * q, make_float4(lr[0], lr[1], lr[2], lr[3]));
                 return;
             }
             const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
@@ -472,13 +474,13 @@ cplx_bwd_kernel(const CplxBwdParams p) {
             for (int e = 0; e < 4; ++e) {
                 hpr[4 * q + e] = hr;
                 hpi[REAL ? 0 : 4 * q + e] = hi;
+                lmr[4 * q + e] = lr[e];
+                lmi[REAL ? 0 : 4 * q + e] = li[e];
                 const float nr = fmaf(lr[e], hr, fmaf(-li[e], hi, sv[e] * brv[e]));
                 const float ni = fmaf(lr[e], hi, fmaf(li[e], hr, sv[e] * biv[e]));
                 hr = nr;
                 hi = ni;
             }
-            st_shared_f4(st + lane * TP + 4 * q, make_float4(lr[0], lr[1], lr[2], lr[3]));
-            st_shared_f4(st + (32 + lane) * TP + 4 * q, make_float4(li[0], li[1], li[2], li[3]));
         };
         // reverse pass of the real operator: eta, lambda, the states and every product are real
         auto reverse_real = [&](const int q) {
@@ -486,9 +488,9 @@ cplx_bwd_kernel(const CplxBwdParams p) {
             const float4 w4 = ld_shared_f4(rows + (c * 3 + 1) * T + 4 * q);
             const float4 br4 = ld_shared_f4(bc + (0 * NL + j) * TP + 4 * q);
             const float4 cr4 = ld_shared_f4(bc + (C::CROW * NL + j) * TP + 4 * q);
-            const float4 lr4 = ld_shared_f4(st + lane * TP + 4 * q);
             const float sv[4] = AUSSM_F4(s4), wv[4] = AUSSM_F4(w4);
-            const float brv[4] = AUSSM_F4(br4), crv[4] = AUSSM_F4(cr4), lr[4] = AUSSM_F4(lr4);
+            const float brv[4] = AUSSM_F4(br4), crv[4] = AUSSM_F4(cr4);
+            const float lr[4] = {lmr[4 * q], lmr[4 * q + 1], lmr[4 * q + 2], lmr[4 * q + 3]};
             const float prv[4] = {hpr[4 * q], hpr[4 * q + 1], hpr[4 * q + 2], hpr[4 * q + 3]};
             float dr[4], E[4], P[4], gBr[4], gCr[4];
 #pragma unroll
@@ -528,12 +530,13 @@ cplx_bwd_kernel(const CplxBwdParams p) {
             const float4 bi4 = ld_shared_f4(bc + (1 * NL + j) * TP + 4 * q);
             const float4 cr4 = ld_shared_f4(bc + (C::CROW * NL + j) * TP + 4 * q);
             const float4 ci4 = ld_shared_f4(bc + (3 * NL + j) * TP + 4 * q);
-            const float4 lr4 = ld_shared_f4(st + lane * TP + 4 * q);
-            const float4 li4 = ld_shared_f4(st + (32 + lane) * TP + 4 * q);
+
             const float sv[4] = AUSSM_F4(s4), wv[4] = AUSSM_F4(w4);
             const float brv[4] = AUSSM_F4(br4), biv[4] = AUSSM_F4(bi4);
             const float crv[4] = AUSSM_F4(cr4), civ[4] = AUSSM_F4(ci4);
-            const float lr[4] = AUSSM_F4(lr4), li[4] = AUSSM_F4(li4);
+            const float lr[4] = {lmr[4 * q], lmr[4 * q + 1], lmr[4 * q + 2], lmr[4 * q + 3]};
+            const float li[4] = {lmi[REAL ? 0 : 4 * q], lmi[REAL ? 0 : 4 * q + 1], lmi[REAL ? 0 : 4 * q + 2],
+                                 lmi[REAL ? 0 : 4 * q + 3]};
             const float prv[4] = {hpr[4 * q], hpr[4 * q + 1], hpr[4 * q + 2], hpr[4 * q + 3]};
             const float piv[4] = {hpi[REAL ? 0 : 4 * q], hpi[REAL ? 0 : 4 * q + 1], hpi[REAL ? 0 : 4 * q + 2],
                                   hpi[REAL ? 0 : 4 * q + 3]};
